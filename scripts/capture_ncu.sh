@@ -12,7 +12,7 @@ for what in ${@:-decode gemm attn}; do
     attnp)  k="regex:attn_prefill_tcgen05_kernel" ;;
     gemm_fp8) k="regex:gemm_fp8_blockscaled_kernel" ;;
   esac
-  timeout 600 ncu --set full --clock-control none --import-source on -k "$k" --launch-skip 2 --launch-count 1 -f \
+  timeout 600 ncu --set full --clock-control none -k "$k" --launch-skip 2 --launch-count 1 -f \
     -o gpurun_out/prof_$what python scripts/profile_targets.py $what > gpurun_out/ncu_$what.log 2>&1
   tail -2 gpurun_out/ncu_$what.log
 done
