@@ -216,11 +216,28 @@ MIXER_KEYS = {
 }
 
 # What an architecture of the family fixes beyond its config.json: the shape of a block ("sandwich": norms before and
-# after each sublayer; "prenorm": one norm before, the sublayer output times ``residual_mult`` added), the kind of
-# its norms, and whether the output head is the embedding table or a tensor of its own.
+# after each sublayer; "prenorm": one norm before, the sublayer output times ``residual_mult`` added; "parallel": one
+# norm whose output both the mixer and the feed-forward read, their outputs summed into the residual), the kind of
+# its norms (``norm_offset`` is added to every block-level norm weight: 1 for weights stored as deviations from one),
+# whether the output head is the embedding table or a tensor of its own, whether a learned position vector joins the
+# token embedding (``positions``), whether each branch of a block has a learned scale per channel (``layer_scale``),
+# and the variant of the grouped-query attention mixer and of the mixture of experts:
+#   attention: mask "window" (the last mask.size positions) | "chunk" (the query's own block of mask.size positions);
+#              sink (a zero-score slot in the softmax denominator); qk_norm "unit" (divide by the RMS) | "weight" (RMS
+#              norm with a learned weight per entry, shared by the heads); bias on q, k, v; gate "head" | "channel";
+#              p32 (softmax weights stay fp32 into the weighted sum of the prompt form)
+#   moe:       router "sigmoid" (independent scores) | "softmax" (over the chosen logits); router_bias; expert "relu2"
+#              (down relu(up x)^2, the score scales the input) | "gated_silu" (down (silu(gate x) * up x), the score
+#              weighs the output); a ``shared`` always-on expert is read from the layer's mlp entry
+_ATTENTION_DEFAULT = {"mask": "window", "sink": False, "qk_norm": "unit", "bias": False, "gate": "head", "p32": False}
+_MOE_DEFAULT = {"router": "sigmoid", "router_bias": False, "expert": "relu2"}
 ARCHITECTURE_TRAITS = {
     "Badapel": {"block": "sandwich", "norm": "layer", "tied_head": True},
     "Vudelix": {"block": "prenorm", "norm": "rms", "tied_head": False},
+    "Labepel": {"block": "parallel", "norm": "rms", "norm_offset": 1.0, "tied_head": True, "positions": "learned",
+                "layer_scale": True,
+                "attention": {"mask": "chunk", "sink": True, "qk_norm": "weight", "bias": True, "gate": "channel", "p32": True},
+                "moe": {"router": "softmax", "router_bias": True, "expert": "gated_silu"}},
 }
 FF_KINDS = ("dense", "moe")
 
@@ -238,7 +255,10 @@ class HybridConfig:
     "router": {"experts": E, "top": k}}``.  ``residual_mult`` scales every sublayer output before it joins the
     residual stream (pre-norm blocks); ``token_side = {"dim": d}`` gives every layer a second, per-layer embedding of
     the current token (a ``d``-wide slice of one table) that is gated by the residual stream and added to it.
-    ``block``, ``norm`` and ``tied_head`` come from :data:`ARCHITECTURE_TRAITS` unless given.
+    ``block``, ``norm``, ``norm_offset``, ``tied_head``, ``positions``, ``layer_scale`` and the mixer variants
+    ``attention`` / ``moe`` come from :data:`ARCHITECTURE_TRAITS` unless given.  ``max_positions`` is the length of the
+    learned position table (``positions = "learned"``).  A mixture of experts may name a ``shared`` expert
+    (``{"ff": n}``) that every token uses.
     """
 
     architecture: str = "Badapel"
@@ -254,6 +274,12 @@ class HybridConfig:
     block: str = ""
     norm: str = ""
     tied_head: Optional[bool] = None
+    max_positions: int = 0
+    norm_offset: Optional[float] = None
+    positions: str = ""
+    layer_scale: Optional[bool] = None
+    attention: Optional[dict] = None
+    moe: Optional[dict] = None
 
     def __post_init__(self) -> None:
         traits = ARCHITECTURE_TRAITS.get(self.architecture, ARCHITECTURE_TRAITS["Badapel"])
@@ -261,8 +287,21 @@ class HybridConfig:
         self.norm = self.norm or traits["norm"]
         if self.tied_head is None:
             self.tied_head = traits["tied_head"]
-        if self.block not in ("sandwich", "prenorm") or self.norm not in ("layer", "rms"):
+        if self.norm_offset is None:
+            self.norm_offset = float(traits.get("norm_offset", 0.0))
+        self.positions = self.positions or traits.get("positions", "none")
+        if self.layer_scale is None:
+            self.layer_scale = bool(traits.get("layer_scale", False))
+        self.attention = {**_ATTENTION_DEFAULT, **traits.get("attention", {}), **(self.attention or {})}
+        self.moe = {**_MOE_DEFAULT, **traits.get("moe", {}), **(self.moe or {})}
+        if self.block not in ("sandwich", "prenorm", "parallel") or self.norm not in ("layer", "rms"):
             raise ValueError(f"unknown block {self.block!r} or norm {self.norm!r}")
+        if self.positions not in ("none", "learned") or (self.positions == "learned" and self.max_positions < 1):
+            raise ValueError("learned positions need max_positions >= 1")
+        if self.attention["mask"] not in ("window", "chunk") or self.attention["qk_norm"] not in ("unit", "weight") \
+                or self.attention["gate"] not in ("head", "channel") or self.moe["router"] not in ("sigmoid", "softmax") \
+                or self.moe["expert"] not in ("relu2", "gated_silu"):
+            raise ValueError(f"unknown attention or mixture-of-experts variant: {self.attention} {self.moe}")
         if self.token_side is not None and int(self.token_side.get("dim", 0)) <= 0:
             raise ValueError("token_side needs a positive dim")
         if self.vocab <= 0 or self.width <= 0 or not self.layers:
@@ -281,6 +320,8 @@ class HybridConfig:
                 r = mlp.get("router", {})
                 if not (1 <= int(r.get("top", 0)) <= int(r.get("experts", 0))) or int(mlp.get("expert", {}).get("ff", 0)) <= 0:
                     raise ValueError(f"layer {i}: a mixture of experts needs expert.ff and 1 <= router.top <= router.experts")
+                if mlp.get("shared") and int(mlp["shared"].get("ff", 0)) <= 0:
+                    raise ValueError(f"layer {i}: a shared expert needs a positive ff")
             m = spec["mixer"]
             if kind in ("attention", "channel_delta") and int(m["heads"]) % int(m["kv_heads"]):
                 raise ValueError(f"layer {i}: heads must be a multiple of kv_heads")
@@ -321,7 +362,8 @@ class HybridConfig:
                    norm_eps=float(d.get("norm", {}).get("eps", 1e-6)),
                    logit_softcap=float(d.get("logit_softcap") or 0.0), name=d.get("name", ""),
                    residual_mult=float(d.get("residual_mult", 1.0)),
-                   token_side=dict(d["token_side"]) if d.get("token_side") else None)
+                   token_side=dict(d["token_side"]) if d.get("token_side") else None,
+                   max_positions=int(d.get("max_positions") or 0))
 
     @classmethod
     def from_file(cls, path: Union[str, Path]) -> "HybridConfig":
@@ -341,6 +383,8 @@ class HybridConfig:
             out["residual_mult"] = self.residual_mult
         if self.token_side is not None:
             out["token_side"] = self.token_side
+        if self.max_positions:
+            out["max_positions"] = self.max_positions
         return out
 
     def save(self, checkpoint_dir: Union[str, Path]) -> Path:

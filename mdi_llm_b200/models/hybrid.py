@@ -35,8 +35,8 @@ import torch.nn as nn
 from ..ops import hybrid as H
 from .config import HybridConfig
 
-__all__ = ["HybridLM", "StatePool", "SandwichBlock", "PreNormBlock", "LatentAttention", "GatedLinearAttention",
-           "ChannelDelta", "WindowAttention", "DenseFF", "MoEFF", "read_safetensors", "write_safetensors", "load_hybrid"]
+__all__ = ["HybridLM", "StatePool", "SandwichBlock", "PreNormBlock", "ParallelBlock", "LatentAttention", "GatedLinearAttention",
+           "ChannelDelta", "WindowAttention", "DenseFF", "GatedFF", "MoEFF", "read_safetensors", "write_safetensors", "load_hybrid"]
 
 _ST_DTYPES = {"BF16": torch.bfloat16, "F32": torch.float32, "F16": torch.float16, "I32": torch.int32, "I64": torch.int64}
 
@@ -293,109 +293,234 @@ class ChannelDelta(nn.Module, _Fused):
 
 
 class WindowAttention(nn.Module, _Fused):
-    """Grouped-query attention over the last ``window`` positions (0: all earlier ones) of the slot's cache."""
+    """Grouped-query attention over cached keys and values of the slot, in the variants an architecture picks
+    (``traits``, see ``models/config.py``): the mask is a sliding window of ``mask.size`` positions or the query's own
+    block of ``mask.size`` positions (no mask entry: every earlier position); q and k are divided by their RMS after an
+    optional rotation, with or without a learned weight per entry; q, k, v may have biases; the softmax may carry a
+    zero-score sink; the output gate is one sigmoid per head or per channel.  A layer whose mixer entry says
+    ``v_mix`` blends its values with those the first such layer computed for the same token,
+    ``v <- (1 - lam) v + lam v_first`` (``lam`` the layer's ``vmix`` scalar; the first such layer keeps its own), and
+    caches the blend."""
 
-    tensor_names = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o"}
-    expand_from = 64   # a step whose every sequence brings at least this many tokens runs as banded matrix products
+    expand_from = 64   # a step whose every sequence brings at least this many tokens runs as batched matrix products
     query_block = 1024  # query rows per band
+    score_bytes = 1 << 28  # fp32 scores alive at a time in the chunked prompt form
 
-    def __init__(self, width: int, m: Dict[str, Any], eps: float) -> None:
+    def __init__(self, width: int, m: Dict[str, Any], eps: float, traits: Optional[Dict[str, Any]] = None) -> None:
         super().__init__()
+        t = {"mask": "window", "sink": False, "qk_norm": "unit", "bias": False, "gate": "head", "p32": False, **(traits or {})}
         self.H, self.G, self.D, self.V = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
         self.scale, self.eps = float(m["scale"]), eps
         self.window = int((m.get("mask") or {}).get("size", 0) or 0)
+        self.mask_kind, self.sink, self.p32 = str(t["mask"]), bool(t["sink"]), bool(t["p32"])
+        self.v_mix = bool(m.get("v_mix"))
         rot = m.get("rot") or {}
         self.nrot, self.rot_base, self.rot_scaling = int(rot.get("dims", 0)), float(rot.get("base", 10000.0)), rot.get("scaling")
         if self.nrot > self.D or self.nrot % 2:
             raise ValueError("rot.dims must be even and at most dim")
         Hh, G, D, V = self.H, self.G, self.D, self.V
         self.q, self.k, self.v = _param(Hh * D, width), _param(G * D, width), _param(G * V, width)
-        self.g, self.o = _param(Hh, width), _param(width, Hh * V)
+        self.g, self.o = _param(Hh if t["gate"] == "head" else Hh * V, width), _param(width, Hh * V)
+        self.tensor_names = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o"}
+        self.has_bias = bool(t["bias"])
+        if self.has_bias:
+            self.q_b, self.k_b, self.v_b = _param(Hh * D), _param(G * D), _param(G * V)
+            self.tensor_names.update({"q.b": "q_b", "k.b": "k_b", "v.b": "v_b"})
+        self.q_norm = self.k_norm = None
+        if t["qk_norm"] == "weight":
+            self.q_norm, self.k_norm = _param(D), _param(D)
+            self.tensor_names.update({"q.norm": "q_norm", "k.norm": "k_norm"})
+        if self.v_mix:
+            self.vmix = nn.Parameter(torch.empty(()), requires_grad=False)
+            self.tensor_names["vmix"] = "vmix"
         self.inv_freq: Optional[torch.Tensor] = None
+        self.b_in: Optional[torch.Tensor] = None
 
     def finalize(self) -> None:
         self.fuse(("q", "k", "v", "g"))
+        if self.has_bias:  # one bias vector for the fused projection; the gate has none
+            self.b_in = torch.cat((self.q_b.data, self.k_b.data, self.v_b.data, torch.zeros_like(self.g.data[:, 0]))).contiguous()
+        if self.v_mix:
+            self.lam = self.vmix.data.reshape(1).contiguous()
         if self.nrot:
             self.inv_freq = H.scaled_inv_freq(self.nrot, self.rot_base, self.rot_scaling, self.q.device)
 
     def forward(self, h: torch.Tensor, plan: H.BatchPlan, st: Dict[str, torch.Tensor]) -> torch.Tensor:
-        p = H.linear(h, self.w_in)
-        q, g = self.col(p, "q"), self.col(p, "g")
-        H.window_append(q, self.col(p, "k"), self.col(p, "v"), self.inv_freq, st["cache"], plan, self.H, self.G, self.D,
-                        self.V, self.nrot, self.eps)
+        p = H.linear(h, self.w_in, self.b_in)
+        q, g, v = self.col(p, "q"), self.col(p, "g"), self.col(p, "v")
+        v_first = lam = None
+        if self.v_mix:
+            v_first = plan.shared.get("v_first")
+            if v_first is None:
+                plan.shared["v_first"] = v  # the first value-mixing layer of the step: later ones blend with these
+            elif v_first.size(1) != v.size(1):
+                raise ValueError("value-mixing layers must agree on kv_heads * vdim")
+            else:
+                lam = self.lam
+        H.window_append(q, self.col(p, "k"), v, self.inv_freq, st["cache"], plan, self.H, self.G, self.D,
+                        self.V, self.nrot, self.eps, self.q_norm, self.k_norm, v_first, lam)
         if min(n for _, n, _, _ in plan.seqs) >= self.expand_from:
-            o = H.head_gate(self._banded(q, st["cache"], plan), g)
+            o = self._chunked(q, st["cache"], plan) if self.mask_kind == "chunk" and self.window > 0 else self._banded(q, st["cache"], plan)
+            o = H.head_gate(o, g) if g.size(1) == self.H else H.headmajor_gate(o, g)
         else:
-            o = H.window_attn(q, g, st["cache"], plan, self.H, self.G, self.D, self.V, self.scale, self.window)
+            o = H.window_attn(q, g, st["cache"], plan, self.H, self.G, self.D, self.V, self.scale, self.window,
+                              mask=self.mask_kind, sink=self.sink)
         return H.linear(o, self.o)
 
+    def _band(self, out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, slot: int, r0: int, p0: int, a: int, b: int,
+              key0: int, window: int) -> None:
+        """Rows ``a..b-1`` of the sequence at ``r0`` against the keys ``key0 .. p0+b-1`` of its slot: scores and the
+        weighted sum as batched matrix products over the key/value heads (the group's query heads stacked as rows),
+        the masked softmax on fp32 scores in between."""
+        Hh, G, D, V = self.H, self.G, self.D, self.V
+        rep, nb = Hh // G, b - a
+        rows = cache[slot, key0:p0 + b]
+        keys = rows.size(0)
+        kt = rows[:, :G * D].view(keys, G, D).permute(1, 2, 0)   # [G, D, keys]
+        vv = rows[:, G * D:].view(keys, G, V).transpose(0, 1)     # [G, keys, V]
+        qh = q[r0 + a:r0 + b].view(nb, G, rep, D).permute(1, 2, 0, 3).reshape(G, rep * nb, D)
+        s = H.matmul_f32(qh, kt).contiguous()
+        pdt = torch.float32 if self.p32 else q.dtype
+        pr = H.causal_softmax(s.view(Hh, nb, keys), p0 + a, self.scale, pdt, window=window, key0=key0, sink=self.sink)
+        out[:, r0 + a:r0 + b] = torch.bmm(pr.view(G, rep * nb, keys), vv.to(pdt)).view(Hh, nb, V)
+
     def _banded(self, q: torch.Tensor, cache: torch.Tensor, plan: H.BatchPlan) -> torch.Tensor:
-        """Prompt form: per block of query rows, scores against the band of keys the block can see and the weighted
-        sum are batched matrix products over the key/value heads (the query heads of a group stacked as rows), the
-        masked softmax runs on fp32 scores.  Returns ``[heads, N, vdim]``."""
-        Hh, G, D, V, W = self.H, self.G, self.D, self.V, self.window
-        rep = Hh // G
-        out = torch.empty(Hh, q.size(0), V, device=q.device, dtype=q.dtype)
+        """Prompt form of the sliding window: per block of query rows, the band of keys the block can see.
+        Returns ``[heads, N, vdim]``."""
+        W = self.window
+        out = torch.empty(self.H, q.size(0), self.V, device=q.device, dtype=q.dtype)
         for r0, n, slot, p0 in plan.seqs:
             for a in range(0, n, self.query_block):
                 b = min(n, a + self.query_block)
-                nb = b - a
-                key0 = max(0, p0 + a - W + 1) if W > 0 else 0
-                rows = cache[slot, key0:p0 + b]
-                keys = rows.size(0)
-                kt = rows[:, :G * D].view(keys, G, D).permute(1, 2, 0)   # [G, D, keys]
-                vv = rows[:, G * D:].view(keys, G, V).transpose(0, 1)     # [G, keys, V]
-                qh = q[r0 + a:r0 + b].view(nb, G, rep, D).permute(1, 2, 0, 3).reshape(G, rep * nb, D)
-                s = H.matmul_f32(qh, kt).contiguous()
-                pr = H.causal_softmax(s.view(Hh, nb, keys), p0 + a, self.scale, q.dtype, window=W, key0=key0)
-                out[:, r0 + a:r0 + b] = torch.bmm(pr.view(G, rep * nb, keys), vv).view(Hh, nb, V)
+                self._band(out, q, cache, slot, r0, p0, a, b, max(0, p0 + a - W + 1) if W > 0 else 0, W)
         return out
+
+    def _chunked(self, q: torch.Tensor, cache: torch.Tensor, plan: H.BatchPlan) -> torch.Tensor:
+        """Prompt form of the chunk mask.  Blocks of ``window`` positions are independent of one another, so the whole
+        blocks a step brings are ONE pair of batched matrix products with (block, key/value head) as the batch and a
+        ``window x window`` causal softmax per block; a step that starts inside a block, or ends inside one, runs
+        that partial block as a band against the block's keys in the cache.  Returns ``[heads, N, vdim]``."""
+        Hh, G, D, V, W = self.H, self.G, self.D, self.V, self.window
+        rep = Hh // G
+        out = torch.empty(Hh, q.size(0), V, device=q.device, dtype=q.dtype)
+        pdt = torch.float32 if self.p32 else q.dtype
+        per = max(1, self.score_bytes // (Hh * W * W * 4))
+        for r0, n, slot, p0 in plan.seqs:
+            head = min(n, (-p0) % W)  # tokens that complete a block begun in an earlier step
+            if head:
+                self._band(out, q, cache, slot, r0, p0, 0, head, (p0 // W) * W, 0)
+            full = (n - head) // W
+            for c0 in range(0, full, per):
+                nc = min(per, full - c0)
+                a = head + c0 * W
+                rows = cache[slot, p0 + a:p0 + a + nc * W]
+                kt = rows[:, :G * D].reshape(nc, W, G, D).permute(0, 2, 3, 1).reshape(nc * G, D, W)
+                vv = rows[:, G * D:].reshape(nc, W, G, V).permute(0, 2, 1, 3).reshape(nc * G, W, V)
+                qh = q[r0 + a:r0 + a + nc * W].reshape(nc, W, G, rep, D).permute(0, 2, 3, 1, 4).reshape(nc * G, rep * W, D)
+                s = H.matmul_f32(qh, kt).contiguous()
+                pr = H.causal_softmax(s.view(nc * Hh, W, W), 0, self.scale, pdt, sink=self.sink)
+                o = torch.bmm(pr.view(nc * G, rep * W, W), vv.to(pdt))  # [nc*G, rep*W, V]
+                out[:, r0 + a:r0 + a + nc * W] = o.view(nc, G, rep, W, V).permute(1, 2, 0, 3, 4).reshape(Hh, nc * W, V)
+            a = head + full * W
+            if a < n:
+                self._band(out, q, cache, slot, r0, p0, a, n, p0 + a, 0)
+        return out
+
+
+class GatedFF(nn.Module, _Fused):
+    """``down (act(gate h) * (up h))`` without biases; gate and up are one matrix product."""
+
+    tensor_names = {"gate": "gate", "up": "up", "down": "down"}
+
+    def __init__(self, width: int, ff: int, act: str = "silu") -> None:
+        super().__init__()
+        self.act = act
+        self.gate, self.up, self.down = _param(ff, width), _param(ff, width), _param(width, ff)
+
+    def finalize(self) -> None:
+        self.fuse(("gate", "up"))
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        return H.linear(H.act_mul(H.linear(h, self.w_in), self.act), self.down)
 
 
 class MoEFF(nn.Module):
-    """``sum over the top-k experts e of down_e relu(up_e (s_e h))^2`` with ``s = sigmoid(router h)`` in fp32.
+    """A mixture of experts: fp32 router logits (optionally with a bias), the ``top`` largest per token, and
 
-    The expert weights are stacked (``up [E, ff, C]``, ``down [E, C, ff]``) at load; the per-expert parameters the
-    checkpoint names become views.  Few tokens (decoding) run two index-driven weight-streaming kernels; many tokens
-    are sorted by expert and run as two grouped matrix products (bf16: one vendor call each, group sizes stay on the
-    device; fp32: one product per expert that received any)."""
+    * ``expert="relu2"``, ``router="sigmoid"``: ``sum_e down_e relu(up_e (s_e h))^2`` with ``s = sigmoid(logit)`` — the
+      score scales the expert's *input*;
+    * ``expert="gated_silu"``, ``router="softmax"``: ``sum_e s_e down_e (silu(gate_e h) * (up_e h))`` with ``s`` the
+      softmax over the chosen logits only — the score weighs the expert's *output*.
+
+    ``shared`` (a :class:`GatedFF`, optional) is an expert every token uses; the block adds its output.  The expert
+    weights are stacked at load (``up [E, ff, C]``, or ``[E, 2 ff, C]`` with an expert's gate rows before its up rows;
+    ``down [E, C, ff]``); the per-expert parameters the checkpoint names become views.  Few tokens (decoding) run two
+    index-driven weight-streaming kernels; many tokens are sorted by expert and run as two grouped matrix products
+    (bf16: one vendor call each, group sizes stay on the device; fp32: one product per expert that received any)."""
 
     gemv_max = 64  # token-expert pairs up to which the index-driven kernels are used
 
-    def __init__(self, width: int, ff: int, experts: int, top: int) -> None:
+    def __init__(self, width: int, ff: int, experts: int, top: int, router: str = "sigmoid", router_bias: bool = False,
+                 expert: str = "relu2", shared_ff: int = 0) -> None:
         super().__init__()
         self.E, self.top, self.ff = int(experts), int(top), int(ff)
+        self.mode, self.gated = router, expert == "gated_silu"
         self.router = _param(self.E, width)
+        self.router_b = _param(self.E) if router_bias else None
         self.e_up = nn.ParameterList([_param(ff, width) for _ in range(self.E)])
         self.e_down = nn.ParameterList([_param(width, ff) for _ in range(self.E)])
+        self.e_gate = nn.ParameterList([_param(ff, width) for _ in range(self.E)]) if self.gated else None
+        self.shared = GatedFF(width, int(shared_ff)) if shared_ff else None
 
     def names(self) -> Dict[str, nn.Parameter]:
         out = {"router": self.router}
+        if self.router_b is not None:
+            out["router.b"] = self.router_b
         for j in range(self.E):
             out[f"e{j}.up"], out[f"e{j}.down"] = self.e_up[j], self.e_down[j]
+            if self.gated:
+                out[f"e{j}.gate"] = self.e_gate[j]
+        if self.shared is not None:
+            for short, attr in self.shared.tensor_names.items():
+                out[f"shared.{short}"] = getattr(self.shared, attr)
         return out
 
     def finalize(self) -> None:
-        self.up = torch.stack([p.data for p in self.e_up]).contiguous()
+        ff = self.ff
+        if self.gated:
+            self.up = torch.stack([torch.cat((g.data, u.data), 0) for g, u in zip(self.e_gate, self.e_up)]).contiguous()
+        else:
+            self.up = torch.stack([p.data for p in self.e_up]).contiguous()
         self.down = torch.stack([p.data for p in self.e_down]).contiguous()
         for j in range(self.E):
-            self.e_up[j].data, self.e_down[j].data = self.up[j], self.down[j]
+            self.e_down[j].data = self.down[j]
+            if self.gated:
+                self.e_gate[j].data, self.e_up[j].data = self.up[j, :ff], self.up[j, ff:]
+            else:
+                self.e_up[j].data = self.up[j]
         self.router32 = self.router.data.float().contiguous()
+        self.router_b32 = None if self.router_b is None else self.router_b.data.float().contiguous()
         self.expert_ids = torch.arange(self.E, device=self.router.device)
+        if self.shared is not None:
+            self.shared.finalize()
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         N, top = h.size(0), self.top
-        idx, wt = H.router_topk(H.linear_f32(h, self.router32), top)
+        idx, wt = H.router_topk(H.linear_f32(h, self.router32, self.router_b32), top, self.mode)
         capturing = h.is_cuda and torch.cuda.is_current_stream_capturing()
         if N * top <= self.gemv_max or capturing:
-            return H.moe_gemv(h, idx, wt, self.up, self.down)
+            return H.moe_gemv(h, idx, wt, self.up, self.down, self.gated)
         flat = idx.view(-1).long()
         order = torch.argsort(flat, stable=True)
         counts = (flat[:, None] == self.expert_ids[None, :]).sum(0)  # stays on the device
-        xin = H.gather_scale_rows(h, (order // top).to(torch.int32), wt.view(-1)[order].contiguous())
-        y = H.grouped_linear(H.relu2_(H.grouped_linear(xin, self.up, counts)), self.down, counts)
+        rows = (order // top).to(torch.int32)
         where = torch.empty_like(order)
         where[order] = torch.arange(order.numel(), device=order.device)
+        if self.gated:
+            mid = H.act_mul(H.grouped_linear(H.gather_scale_rows(h, rows), self.up, counts))
+            return H.combine_rows(H.grouped_linear(mid, self.down, counts), where.to(torch.int32), N, top, wt)
+        xin = H.gather_scale_rows(h, rows, wt.view(-1)[order].contiguous())
+        y = H.grouped_linear(H.relu2_(H.grouped_linear(xin, self.up, counts)), self.down, counts)
         return H.combine_rows(y, where.to(torch.int32), N, top)
 
 
@@ -490,6 +615,40 @@ class PreNormBlock(nn.Module):
             self.side(x, tokens, side_table, self.eps, self.mult, dtype)
 
 
+class ParallelBlock(nn.Module):
+    """``x += ls1 * mixer(h) + ls2 * (ff(h) + shared(h))`` with ``h = norm1(x)``: one norm, read by both branches,
+    each branch with a learned scale per channel when the architecture has them.  ``norm_offset`` is added to the
+    norm weight (1: the weight is stored as its deviation from one)."""
+
+    side = None
+
+    def __init__(self, width: int, mixer: nn.Module, ff: Optional[nn.Module], eps: float, norm: str, norm_offset: float,
+                 layer_scale: bool) -> None:
+        super().__init__()
+        self.mix, self.mlp, self.eps, self.kind, self.offset = mixer, ff, eps, norm, float(norm_offset)
+        self.norm1 = _LN(width) if norm == "layer" else _RMS(width)
+        self.ls1 = _param(width) if layer_scale else None
+        self.ls2 = _param(width) if layer_scale and ff is not None else None
+
+    def norm_names(self) -> List[str]:
+        return ["norm1"]
+
+    def extra_tensors(self) -> Dict[str, nn.Parameter]:
+        return {k: p for k, p in (("ls1", self.ls1), ("ls2", self.ls2)) if p is not None}
+
+    def forward(self, x: torch.Tensor, plan: H.BatchPlan, st: Dict[str, torch.Tensor], dtype: torch.dtype,
+                tokens: Optional[torch.Tensor] = None, side_table: Optional[torch.Tensor] = None) -> None:
+        h = H.norm_rows(x, self.norm1.w, self.norm1.b, self.eps, self.kind, dtype, self.offset)
+        a = self.mix(h, plan, st)
+        b = b2 = None
+        if self.mlp is not None:
+            b = self.mlp(h)
+            shared = getattr(self.mlp, "shared", None)
+            if shared is not None:
+                b2 = shared(h)
+        H.scaled_branches(x, a, self.ls1, b, b2, self.ls2)
+
+
 def _rank_of(tensors: Optional[Dict[str, torch.Tensor]], key: str, default: int) -> int:
     return int(tensors[key].shape[0]) if tensors is not None and key in tensors else default
 
@@ -508,6 +667,7 @@ class HybridLM(nn.Module):
         ranks = ranks or {}
         C, eps = config.width, config.norm_eps
         self.embed = _param(config.vocab, C)
+        self.pos = _param(config.max_positions, C) if config.positions == "learned" else None
         self.loop_in = _param(C, 2 * C) if config.loop is not None else None
         blocks = []
         for i, spec in enumerate(config.layers):
@@ -515,7 +675,7 @@ class HybridLM(nn.Module):
             if kind == "latent_attention":
                 mixer: nn.Module = LatentAttention(C, m, eps)
             elif kind == "attention":
-                mixer = WindowAttention(C, m, eps)
+                mixer = WindowAttention(C, m, eps, config.attention)
             elif kind == "gla":
                 mixer = GatedLinearAttention(C, m, eps, ranks.get(f"l{i}.mix.a1", 16))
             else:
@@ -524,11 +684,14 @@ class HybridLM(nn.Module):
             if not mlp:
                 ff: Optional[nn.Module] = None
             elif mlp["kind"] == "moe":
-                ff = MoEFF(C, mlp["expert"]["ff"], mlp["router"]["experts"], mlp["router"]["top"])
+                ff = MoEFF(C, mlp["expert"]["ff"], mlp["router"]["experts"], mlp["router"]["top"], config.moe["router"],
+                           config.moe["router_bias"], config.moe["expert"], int((mlp.get("shared") or {}).get("ff", 0)))
             else:
                 ff = DenseFF(C, mlp["ff"])
             if config.block == "sandwich":
                 blocks.append(SandwichBlock(C, mixer, ff, eps))
+            elif config.block == "parallel":
+                blocks.append(ParallelBlock(C, mixer, ff, eps, config.norm, config.norm_offset, config.layer_scale))
             else:
                 sd = int(config.token_side["dim"]) if config.token_side else 0
                 side = TokenSide(C, sd, i * sd) if sd else None
@@ -547,6 +710,8 @@ class HybridLM(nn.Module):
             out["final.norm.b"] = self.final_norm.b
         if self.loop_in is not None:
             out["loop.in"] = self.loop_in
+        if self.pos is not None:
+            out["pos"] = self.pos
         if self.side_embed is not None:
             out["side.embed"] = self.side_embed
         if self.head_w is not None:
@@ -558,6 +723,9 @@ class HybridLM(nn.Module):
                     out[f"l{i}.{n}.b"] = getattr(blk, n).b
             for short, attr in blk.mix.tensor_names.items():
                 out[f"l{i}.mix.{short}"] = getattr(blk.mix, attr)
+            if hasattr(blk, "extra_tensors"):
+                for short, prm in blk.extra_tensors().items():
+                    out[f"l{i}.{short}"] = prm
             if isinstance(blk.mlp, MoEFF):
                 for short, prm in blk.mlp.names().items():
                     out[f"l{i}.mlp.{short}"] = prm
@@ -570,7 +738,11 @@ class HybridLM(nn.Module):
 
     def load_tensors(self, tensors: Dict[str, torch.Tensor], device: Union[str, torch.device], dtype: torch.dtype) -> "HybridLM":
         tm = self.tensor_map()
-        missing, extra = sorted(set(tm) - set(tensors)), sorted(set(tensors) - set(tm))
+        # a checkpoint may carry tensors a layer has no use for (a mixing factor where nothing is mixed, the scale of
+        # a feed-forward the layer does not have)
+        unused = (".mix.vmix", ".ls2")
+        missing = sorted(set(tm) - set(tensors))
+        extra = sorted(n for n in set(tensors) - set(tm) if not n.endswith(unused))
         if missing or extra:
             raise KeyError(f"checkpoint does not match the configuration: missing {missing[:5]}, unexpected {extra[:5]}")
         for name, p in tm.items():
@@ -590,8 +762,12 @@ class HybridLM(nn.Module):
                 t = torch.randn(p.shape, generator=gen) * 0.5
             elif name.endswith(".b") and p.dim() == 1 and "norm" in name:
                 t = torch.randn(p.shape, generator=gen) * 0.1
-            elif "norm" in name:
+            elif "norm" in name and not name.endswith((".q.norm", ".k.norm")):
+                t = (1.0 - self.config.norm_offset) + torch.randn(p.shape, generator=gen) * 0.1
+            elif "norm" in name or name.endswith((".ls1", ".ls2")):
                 t = 1.0 + torch.randn(p.shape, generator=gen) * 0.1
+            elif name.endswith(".vmix"):
+                t = torch.rand(p.shape, generator=gen) * 0.5 + 0.25
             else:
                 t = torch.randn(p.shape, generator=gen) * 0.5
             if name == "embed":
@@ -602,7 +778,7 @@ class HybridLM(nn.Module):
     def finalize(self) -> "HybridLM":
         for blk in self.blocks:
             blk.mix.finalize()
-            if isinstance(blk.mlp, MoEFF):
+            if isinstance(blk.mlp, (MoEFF, GatedFF)):
                 blk.mlp.finalize()
         self.dtype, self.device = self.embed.dtype, self.embed.device
         return self
@@ -622,7 +798,10 @@ class HybridLM(nn.Module):
         for _, n, slot, p0 in plan.seqs:
             if p0 + n > pool.max_seq_length:
                 raise ValueError(f"sequence of {p0 + n} tokens exceeds the pool's max_seq_length {pool.max_seq_length}")
-        x0 = H.embed_rows(self.embed, tokens)
+            if self.pos is not None and p0 + n > self.pos.size(0):
+                raise ValueError(f"sequence of {p0 + n} tokens exceeds the model's {self.pos.size(0)} learned positions")
+        plan.shared.clear()
+        x0 = H.embed_rows(self.embed, tokens, self.pos, plan)
         x = x0.clone() if self.loop_in is not None else x0
         for run, (li, first) in enumerate(self.runs):
             if first:
@@ -642,7 +821,8 @@ class HybridLM(nn.Module):
     @torch.inference_mode()
     def head(self, x: torch.Tensor) -> torch.Tensor:
         """fp32 logits of residual rows ``x [n, width]``: final norm, output head (tied or its own), soft cap."""
-        h = H.norm_rows(x, self.final_norm.w, self.final_norm.b, self.config.norm_eps, self.config.norm, self.dtype)
+        h = H.norm_rows(x, self.final_norm.w, self.final_norm.b, self.config.norm_eps, self.config.norm, self.dtype,
+                        self.config.norm_offset)
         return H.softcap(H.linear(h, self.embed if self.head_w is None else self.head_w), self.config.logit_softcap)
 
     def forward(self, tokens: torch.Tensor, plan: H.BatchPlan, pool: StatePool, rows: Optional[Sequence[int]] = None,

@@ -266,6 +266,7 @@ def lookup(name: str) -> Dict[str, Any]:
 architectures: Dict[str, Tuple[str, str]] = {
     "Badapel": ("mdi_llm_b200.models.config:HybridConfig", "mdi_llm_b200.models.hybrid:HybridLM"),
     "Vudelix": ("mdi_llm_b200.models.config:HybridConfig", "mdi_llm_b200.models.hybrid:HybridLM"),
+    "Labepel": ("mdi_llm_b200.models.config:HybridConfig", "mdi_llm_b200.models.hybrid:HybridLM"),
 }
 
 

@@ -68,11 +68,20 @@ __device__ __forceinline__ float gelu_erff_(float x) { return 0.5f * x * (1.f + 
 // ---------------------------------------------------------------------------------------------------------
 // rows: embedding gather, casts, norms, element-wise epilogues
 // ---------------------------------------------------------------------------------------------------------
+// x[t] = table[tokens[t]] (+ pos_table[position of t] when the model has learned positions), in fp32.
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ x,
-                                  int C) {
-  const T* src = table + (size_t)tokens[blockIdx.x] * C;
-  float* dst = x + (size_t)blockIdx.x * C;
+                                  int C, const T* __restrict__ pos_table, const int* __restrict__ meta,
+                                  const int* __restrict__ tok_seq) {
+  int t = blockIdx.x;
+  const T* src = table + (size_t)tokens[t] * C;
+  float* dst = x + (size_t)t * C;
+  if (pos_table) {
+    const int* m = meta + 4 * tok_seq[t];
+    const T* pr = pos_table + (size_t)(m[3] + (t - m[0])) * C;
+    for (int i = threadIdx.x; i < C; i += blockDim.x) dst[i] = to_f(src[i]) + to_f(pr[i]);
+    return;
+  }
   for (int i = threadIdx.x; i < C; i += blockDim.x) dst[i] = to_f(src[i]);
 }
 
@@ -86,11 +95,11 @@ __global__ void cast_rows_kernel(const Tin* __restrict__ in, long long in_stride
 
 // kind 0: (x - mean) / sqrt(var + eps) * w + b      kind 1: x / sqrt(mean(x^2) + eps) * w
 // kind 2: x (no normalisation).  accumulate != 0: out (fp32) += scale * result, the residual update of a block;
-// else out = result.
+// else out = result.  The weight applied is w_offset + w (w_offset = 1: a weight stored as its deviation from one).
 template <typename Tin, typename Tw, typename Tout>
 __global__ void norm_rows_kernel(const Tin* __restrict__ in, long long in_stride, const Tw* __restrict__ w,
                                  const Tw* __restrict__ b, Tout* __restrict__ out, long long out_stride, int n,
-                                 float eps, int kind, int accumulate, float scale) {
+                                 float eps, int kind, int accumulate, float scale, float w_offset) {
   __shared__ float red[33];
   const Tin* src = in + (size_t)blockIdx.x * in_stride;
   Tout* dst = out + (size_t)blockIdx.x * out_stride;
@@ -116,7 +125,7 @@ __global__ void norm_rows_kernel(const Tin* __restrict__ in, long long in_stride
   float inv = 1.f / sqrtf(block_sum(ss, red) / n + eps);
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     float y = (to_f(src[i]) - mean) * inv;
-    if (w) y *= to_f(w[i]);
+    if (w) y *= w_offset + to_f(w[i]);
     if (b) y += to_f(b[i]);
     if (accumulate) dst[i] = from_f<Tout>(to_f(dst[i]) + scale * y);
     else dst[i] = from_f<Tout>(y);
@@ -329,9 +338,10 @@ __global__ void latent_combine_kernel(const float* __restrict__ part_acc, const 
 
 // Causal softmax of fp32 score rows for the expanded (prompt) form of latent attention: row (h, i) sees keys
 // j <= first_pos + i; p = softmax(scale * s) over those, zeros elsewhere, written in the activation type.
+// sink != 0: one more slot of score zero joins the denominator (it has no value): p_j = e^{s_j} / (1 + sum e^{s_k}).
 template <typename T>
 __global__ void causal_softmax_kernel(const float* __restrict__ s, T* __restrict__ p, int rows_per_head, int keys,
-                                      int first_pos, float scale, int window, int key0) {
+                                      int first_pos, float scale, int window, int key0, int sink) {
   __shared__ float red[33];
   size_t row = blockIdx.x;
   int i = (int)(row % rows_per_head);
@@ -348,9 +358,11 @@ __global__ void causal_softmax_kernel(const float* __restrict__ s, T* __restrict
   __syncthreads();
   m = -INFINITY;
   for (int w = 0; w < (blockDim.x + 31) / 32; ++w) m = fmaxf(m, red[w]);
+  if (sink) m = fmaxf(m, 0.f);  // scale > 0: the shift that keeps every exponent <= 0
   float sum = 0.f;
   for (int j = lo + threadIdx.x; j < vis; j += blockDim.x) sum += expf((src[j] - m) * scale);
   sum = block_sum(sum, red);
+  if (sink) sum += expf(-m * scale);
   float inv = 1.f / sum;
   for (int j = threadIdx.x; j < keys; j += blockDim.x)
     dst[j] = from_f<T>(j >= lo && j < vis ? expf((src[j] - m) * scale) * inv : 0.f);
@@ -728,10 +740,15 @@ using namespace hyb;
 extern "C" {
 
 // dtype codes: 0 = bf16, 1 = fp32
-int hyb_embed_rows(const void* table, const int* tokens, float* x, int N, int C, int dt, cudaStream_t st) {
+int hyb_embed_rows(const void* table, const int* tokens, float* x, int N, int C, const void* pos_table,
+                   const int* meta, const int* tok_seq, int dt, cudaStream_t st) {
   if (N == 0) return 0;
-  HYB_DISPATCH(dt, (embed_rows_kernel<bf16><<<N, 256, 0, st>>>((const bf16*)table, tokens, x, C)),
-               (embed_rows_kernel<float><<<N, 256, 0, st>>>((const float*)table, tokens, x, C)));
+  if (pos_table && (!meta || !tok_seq)) return -2;
+  HYB_DISPATCH(dt,
+               (embed_rows_kernel<bf16><<<N, 256, 0, st>>>((const bf16*)table, tokens, x, C, (const bf16*)pos_table, meta,
+                                                           tok_seq)),
+               (embed_rows_kernel<float><<<N, 256, 0, st>>>((const float*)table, tokens, x, C, (const float*)pos_table,
+                                                            meta, tok_seq)));
   return (int)cudaGetLastError();
 }
 
@@ -753,11 +770,11 @@ int hyb_cast_rows(const void* in, long long in_stride, int in_dt, void* out, lon
 // {bf16, fp32}.
 int hyb_norm_rows(const void* in, long long in_stride, int in_dt, const void* w, const void* b, int w_dt, void* out,
                   long long out_stride, int out_dt, int rows, int n, float eps, int kind, int accumulate, float scale,
-                  cudaStream_t st) {
+                  float w_offset, cudaStream_t st) {
   if (rows == 0) return 0;
 #define NR(TI, TW, TO)                                                                                              \
   norm_rows_kernel<TI, TW, TO><<<rows, 256, 0, st>>>((const TI*)in, in_stride, (const TW*)w, (const TW*)b, (TO*)out, \
-                                                      out_stride, n, eps, kind, accumulate, scale)
+                                                      out_stride, n, eps, kind, accumulate, scale, w_offset)
   if (w_dt == 1) {
     if (in_dt != 1 || out_dt != 1) return -3;
     NR(float, float, float);
@@ -840,11 +857,11 @@ int hyb_latent_attn(const void* qlat, const void* q, long long q_stride, const v
 }
 
 int hyb_causal_softmax(const float* s, void* p, long long rows, int rows_per_head, int keys, int first_pos, float scale,
-                       int window, int key0, int dt, cudaStream_t st) {
+                       int window, int key0, int sink, int dt, cudaStream_t st) {
   if (rows == 0) return 0;
   if (scale <= 0.f) return -3;  // the row maximum is taken before scaling
-  HYB_DISPATCH(dt, (causal_softmax_kernel<bf16><<<(unsigned)rows, 256, 0, st>>>(s, (bf16*)p, rows_per_head, keys, first_pos, scale, window, key0)),
-               (causal_softmax_kernel<float><<<(unsigned)rows, 256, 0, st>>>(s, (float*)p, rows_per_head, keys, first_pos, scale, window, key0)));
+  HYB_DISPATCH(dt, (causal_softmax_kernel<bf16><<<(unsigned)rows, 256, 0, st>>>(s, (bf16*)p, rows_per_head, keys, first_pos, scale, window, key0, sink)),
+               (causal_softmax_kernel<float><<<(unsigned)rows, 256, 0, st>>>(s, (float*)p, rows_per_head, keys, first_pos, scale, window, key0, sink)));
   return (int)cudaGetLastError();
 }
 
@@ -964,12 +981,16 @@ __device__ __forceinline__ float gelu_tanhf_(float z) {
 // One block per token.  Warps walk the H query heads and then the G key heads: rotate the first `nrot` entries
 // (entry 2i with 2i+1, angle pos * inv_freq[i]), divide the head by its root mean square over D, store queries
 // in place and keys into the slot's cache row; the values are copied behind the keys.  D <= 256.
+// qw / kw (optional, [D], shared by the heads) multiply the normalised query / key.  With `lam` the value written is
+// (1 - lam) * v + lam * v_first, the blend with another layer's values of the same token, evaluated in fp32.
 #define WA_MAXD 8
 template <typename T>
 __global__ void window_append_kernel(T* __restrict__ q, long long q_stride, const T* __restrict__ k, long long k_stride,
                                      const T* __restrict__ v, long long v_stride, const float* __restrict__ inv_freq,
                                      T* __restrict__ cache, long long slot_stride, const int* __restrict__ meta,
-                                     const int* __restrict__ tok_seq, int H, int G, int D, int V, int nrot, float eps) {
+                                     const int* __restrict__ tok_seq, int H, int G, int D, int V, int nrot, float eps,
+                                     const T* __restrict__ qw, const T* __restrict__ kw, const T* __restrict__ v_first,
+                                     long long vf_stride, const T* __restrict__ lam) {
   int t = blockIdx.x;
   const int* m = meta + 4 * tok_seq[t];
   int pos = m[3] + (t - m[0]);
@@ -979,6 +1000,7 @@ __global__ void window_append_kernel(T* __restrict__ q, long long q_stride, cons
   for (int hv = w; hv < H + G; hv += nw) {
     const T* src = hv < H ? q + (size_t)t * q_stride + (size_t)hv * D : k + (size_t)t * k_stride + (size_t)(hv - H) * D;
     T* dst = hv < H ? q + (size_t)t * q_stride + (size_t)hv * D : row + (size_t)(hv - H) * D;
+    const T* nw_ = hv < H ? qw : kw;
     float y[WA_MAXD];
     float ss = 0.f;
 #pragma unroll
@@ -1001,11 +1023,17 @@ __global__ void window_append_kernel(T* __restrict__ q, long long q_stride, cons
 #pragma unroll
     for (int c = 0; c < WA_MAXD; ++c) {
       int d = lane + 32 * c;
-      if (d < D) dst[d] = from_f<T>(y[c] * inv);
+      if (d < D) dst[d] = from_f<T>(nw_ ? y[c] * inv * to_f(nw_[d]) : y[c] * inv);
     }
   }
   const T* vs = v + (size_t)t * v_stride;
   T* vd = row + (size_t)G * D;
+  if (lam) {
+    float l = to_f(lam[0]);
+    const T* vf = v_first + (size_t)t * vf_stride;
+    for (int i = threadIdx.x; i < G * V; i += blockDim.x) vd[i] = from_f<T>((1.f - l) * to_f(vs[i]) + l * to_f(vf[i]));
+    return;
+  }
   for (int i = threadIdx.x; i < G * V; i += blockDim.x) vd[i] = vs[i];
 }
 
@@ -1014,6 +1042,9 @@ __global__ void window_append_kernel(T* __restrict__ q, long long q_stride, cons
 // and the weighted sum are fp32; the result is multiplied by sigmoid(gate) per head.  V <= 256.
 // With nsplit > 1 (few tokens: decoding) block z takes every nsplit-th tile and leaves its unnormalised sum, running
 // maximum and denominator in part_acc / part_ml; window_combine_kernel merges the shares and applies the gate.
+// mask_kind 0: the last `window` positions (0 = all earlier ones); 1: the positions of the token's own block of `window`
+// positions, blocks counted from position 0 of the sequence.  sink != 0: a slot of score zero without a value joins the
+// softmax denominator.  gate_mode 1: sigmoid(gate[t, h]) per head; 2: sigmoid(gate[t, h * V + d]) per output channel.
 #define WT_TILE 32
 #define WT_MAXV 8
 template <typename T>
@@ -1021,7 +1052,8 @@ __global__ void window_attn_kernel(const T* __restrict__ q, long long q_stride, 
                                    long long g_stride, const T* __restrict__ cache, long long slot_stride,
                                    const int* __restrict__ meta, const int* __restrict__ tok_seq, T* __restrict__ out,
                                    int H, int G, int D, int V, float scale, int window, int nsplit,
-                                   float* __restrict__ part_acc, float* __restrict__ part_ml) {
+                                   float* __restrict__ part_acc, float* __restrict__ part_ml, int mask_kind, int sink,
+                                   int gate_mode) {
   extern __shared__ float sm[];
   int rep = H / G;
   float* qs = sm;                       // [rep][D]
@@ -1030,7 +1062,7 @@ __global__ void window_attn_kernel(const T* __restrict__ q, long long q_stride, 
   int t = blockIdx.x, g = blockIdx.y;
   const int* m = meta + 4 * tok_seq[t];
   int pos = m[3] + (t - m[0]);
-  int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  int lo = window > 0 ? (mask_kind == 1 ? (pos / window) * window : max(0, pos - window + 1)) : 0;
   const T* base = cache + (size_t)m[2] * slot_stride;
   int rowlen = G * (D + V);
   int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
@@ -1087,12 +1119,22 @@ __global__ void window_attn_kernel(const T* __restrict__ q, long long q_stride, 
     if (lane == 0) { part_ml[2 * row] = mx; part_ml[2 * row + 1] = l; }
     return;
   }
-  float gt = gate ? sigmoidf_(to_f(gate[(size_t)t * g_stride + h])) : 1.f;
+  if (sink) {  // the zero-score slot: shift to max(mx, 0), add its weight to the denominator
+    float mn = fmaxf(mx, 0.f), corr = expf(mx - mn);
+    l = l * corr + expf(-mn);
+#pragma unroll
+    for (int c = 0; c < WT_MAXV; ++c) acc[c] *= corr;
+  }
+  float gt = gate && gate_mode == 1 ? sigmoidf_(to_f(gate[(size_t)t * g_stride + h])) : 1.f;
   float inv = gt / l;
 #pragma unroll
   for (int c = 0; c < WT_MAXV; ++c) {
     int d = lane + 32 * c;
-    if (d < V) out[(size_t)t * H * V + (size_t)h * V + d] = from_f<T>(acc[c] * inv);
+    if (d < V) {
+      float o = acc[c] * inv;
+      if (gate && gate_mode == 2) o *= sigmoidf_(to_f(gate[(size_t)t * g_stride + (size_t)h * V + d]));
+      out[(size_t)t * H * V + (size_t)h * V + d] = from_f<T>(o);
+    }
   }
 }
 
@@ -1100,23 +1142,25 @@ __global__ void window_attn_kernel(const T* __restrict__ q, long long q_stride, 
 template <typename T>
 __global__ void window_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                       const T* __restrict__ gate, long long g_stride, T* __restrict__ out, int N, int H,
-                                      int V, int nsplit) {
+                                      int V, int nsplit, int sink, int gate_mode) {
   int t = blockIdx.x, h = blockIdx.y;
-  float M = -INFINITY;
+  float M = sink ? 0.f : -INFINITY;
   for (int s = 0; s < nsplit; ++s) M = fmaxf(M, part_ml[2 * (((size_t)s * N + t) * H + h)]);
-  float l = 0.f;
+  float l = sink ? expf(-M) : 0.f;
   for (int s = 0; s < nsplit; ++s) {
     size_t row = ((size_t)s * N + t) * H + h;
     l += part_ml[2 * row + 1] * expf(part_ml[2 * row] - M);
   }
-  float gt = gate ? sigmoidf_(to_f(gate[(size_t)t * g_stride + h])) : 1.f;
+  float gt = gate && gate_mode == 1 ? sigmoidf_(to_f(gate[(size_t)t * g_stride + h])) : 1.f;
   for (int d = threadIdx.x; d < V; d += blockDim.x) {
     float a = 0.f;
     for (int s = 0; s < nsplit; ++s) {
       size_t row = ((size_t)s * N + t) * H + h;
       a += part_acc[row * V + d] * expf(part_ml[2 * row] - M);
     }
-    out[(size_t)t * H * V + (size_t)h * V + d] = from_f<T>(a * gt / l);
+    float o = a * gt / l;
+    if (gate && gate_mode == 2) o *= sigmoidf_(to_f(gate[(size_t)t * g_stride + (size_t)h * V + d]));
+    out[(size_t)t * H * V + (size_t)h * V + d] = from_f<T>(o);
   }
 }
 
@@ -1144,9 +1188,10 @@ __global__ void token_side_gate_kernel(const T* __restrict__ z, long long z_stri
     out[(size_t)r * d + c] = from_f<T>(gelu_tanhf_(to_f(z[(size_t)r * z_stride + c])) * to_f(e[c]));
 }
 
-// One thread per token: the `top` largest logits (ties to the lower index), scores = sigmoid(logit).
+// One thread per token: the `top` largest logits (ties to the lower index).  mode 0: scores = sigmoid(logit), each
+// on its own; mode 1: scores = softmax over the chosen logits only.
 __global__ void router_topk_kernel(const float* __restrict__ z, int* __restrict__ idx, float* __restrict__ wt, int N,
-                                   int E, int top) {
+                                   int E, int top, int mode) {
   int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= N) return;
   const float* row = z + (size_t)t * E;
@@ -1160,7 +1205,13 @@ __global__ void router_topk_kernel(const float* __restrict__ z, int* __restrict_
       if (!taken && (best < 0 || v > bv)) { best = e; bv = v; }
     }
     idx[(size_t)t * top + k] = best;
-    wt[(size_t)t * top + k] = sigmoidf_(bv);
+    wt[(size_t)t * top + k] = mode == 0 ? sigmoidf_(bv) : bv;
+  }
+  if (mode == 1) {  // the first choice holds the largest logit
+    float* w = wt + (size_t)t * top;
+    float m = w[0], sum = 0.f;
+    for (int k = 0; k < top; ++k) { w[k] = expf(w[k] - m); sum += w[k]; }
+    for (int k = 0; k < top; ++k) w[k] /= sum;
   }
 }
 
@@ -1185,6 +1236,8 @@ __device__ __forceinline__ float dot_row(const T* __restrict__ wrow, const float
 // cross the memory system once however many pairs share it; experts nobody chose cost one scan of idx.
 //   MODE 0 (up):   y[p, f] = relu(w[e][f, :] . round_T(wt[p] * x[p / top, :]))^2     x in T, K = width
 //   MODE 1 (down): y[p, c] = w[e][c, :] . a[p, :]                                    a fp32, K = ff
+//   MODE 2 (gated up): y[p, f] = silu(w[e][f, :] . x) * (w[e][R + f, :] . x), x = x[p / top, :] unscaled; an expert's
+//                  matrix is [2R, K], its gate rows first and its up rows behind them
 #define MOE_ROWS 32
 #define MOE_PCH 4
 template <typename T, int MODE>
@@ -1196,7 +1249,7 @@ __global__ void moe_pairs_kernel(const void* __restrict__ xin, long long x_strid
   __shared__ int s_cnt, s_next;
   int e = blockIdx.x;
   int lane = threadIdx.x & 31, wp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  const T* we = w + (size_t)e * R * K;
+  const T* we = w + (size_t)e * (MODE == 2 ? 2 : 1) * R * K;
   if (threadIdx.x == 0) s_next = 0;
   __syncthreads();
   while (true) {
@@ -1216,6 +1269,9 @@ __global__ void moe_pairs_kernel(const void* __restrict__ xin, long long x_strid
         const T* x = (const T*)xin + (size_t)(p / top) * x_stride;
         float sc = wt[p];
         for (int c = threadIdx.x; c < K; c += blockDim.x) sm[m * K + c] = to_f(from_f<T>(sc * to_f(x[c])));
+      } else if (MODE == 2) {
+        const T* x = (const T*)xin + (size_t)(p / top) * x_stride;
+        for (int c = threadIdx.x; c < K; c += blockDim.x) sm[m * K + c] = to_f(x[c]);
       } else {
         const float* x = (const float*)xin + (size_t)p * x_stride;
         for (int c = threadIdx.x; c < K; c += blockDim.x) sm[m * K + c] = x[c];
@@ -1226,7 +1282,15 @@ __global__ void moe_pairs_kernel(const void* __restrict__ xin, long long x_strid
       int f = blockIdx.y * MOE_ROWS + r;
       if (f >= R) break;
       const T* wrow = we + (size_t)f * K;
-      float acc[MOE_PCH];
+      float acc[MOE_PCH], first[MOE_PCH];
+#pragma unroll
+      for (int m = 0; m < MOE_PCH; ++m) first[m] = 0.f;
+      for (int half = 0; half < (MODE == 2 ? 2 : 1); ++half) {
+      if (half == 1) {
+        wrow += (size_t)R * K;
+#pragma unroll
+        for (int m = 0; m < MOE_PCH; ++m) first[m] = acc[m];
+      }
 #pragma unroll
       for (int m = 0; m < MOE_PCH; ++m) acc[m] = 0.f;
       if ((K & 7) == 0) {
@@ -1259,12 +1323,15 @@ __global__ void moe_pairs_kernel(const void* __restrict__ xin, long long x_strid
             if (m < cnt) acc[m] += wv * sm[m * K + c];
         }
       }
+      }
 #pragma unroll
       for (int m = 0; m < MOE_PCH; ++m) {
         if (m < cnt) {
           float v = warp_sum(acc[m]);
+          float g = MODE == 2 ? warp_sum(first[m]) : 0.f;
           if (lane == 0) {
             if (MODE == 0) { v = fmaxf(v, 0.f); v = v * v; }
+            if (MODE == 2) v *= siluf_(g);
             y[(size_t)match[m] * R + f] = v;
           }
         }
@@ -1274,13 +1341,14 @@ __global__ void moe_pairs_kernel(const void* __restrict__ xin, long long x_strid
   }
 }
 
-// out[t, c] = sum_k y[t * top + k, c], summed in the order of k.
+// out[t, c] = sum_k wt[t * top + k] * y[t * top + k, c] (wt absent: plain sum), summed in the order of k.
 template <typename T>
-__global__ void moe_sum_kernel(const float* __restrict__ y, T* __restrict__ out, int top, int C) {
+__global__ void moe_sum_kernel(const float* __restrict__ y, const float* __restrict__ wt, T* __restrict__ out, int top,
+                               int C) {
   int t = blockIdx.x;
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
     float a = 0.f;
-    for (int k = 0; k < top; ++k) a += y[((size_t)t * top + k) * C + c];
+    for (int k = 0; k < top; ++k) a += (wt ? wt[(size_t)t * top + k] : 1.f) * y[((size_t)t * top + k) * C + c];
     out[(size_t)t * C + c] = from_f<T>(a);
   }
 }
@@ -1290,18 +1358,57 @@ __global__ void gather_scale_rows_kernel(const T* __restrict__ h, long long h_st
                                          const float* __restrict__ scale, T* __restrict__ out, int C) {
   int i = blockIdx.x;
   const T* src = h + (size_t)rows[i] * h_stride;
+  if (!scale) {
+    for (int c = threadIdx.x; c < C; c += blockDim.x) out[(size_t)i * C + c] = src[c];
+    return;
+  }
   float w = scale[i];
   for (int c = threadIdx.x; c < C; c += blockDim.x) out[(size_t)i * C + c] = from_f<T>(w * to_f(src[c]));
 }
 
 template <typename T>
-__global__ void combine_rows_kernel(const T* __restrict__ y, const int* __restrict__ where, T* __restrict__ out, int top,
-                                    int C) {
+__global__ void combine_rows_kernel(const T* __restrict__ y, const int* __restrict__ where, const float* __restrict__ wt,
+                                    T* __restrict__ out, int top, int C) {
   int t = blockIdx.x;
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
     float a = 0.f;
-    for (int k = 0; k < top; ++k) a += to_f(y[(size_t)where[(size_t)t * top + k] * C + c]);
+    for (int k = 0; k < top; ++k)
+      a += (wt ? wt[(size_t)t * top + k] : 1.f) * to_f(y[(size_t)where[(size_t)t * top + k] * C + c]);
     out[(size_t)t * C + c] = from_f<T>(a);
+  }
+}
+
+// out[r, f] = act(in[r, f]) * in[r, F + f]: the product of a gated feed-forward whose gate and up projections are
+// the two halves of one row.  act 0: silu, 1: gelu (tanh form).
+template <typename T>
+__global__ void act_mul_rows_kernel(const T* __restrict__ in, long long in_stride, T* __restrict__ out, int F, int act,
+                                    long long total) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  long long r = i / F;
+  int f = (int)(i - r * F);
+  const T* row = in + (size_t)r * in_stride;
+  float g = to_f(row[f]), u = to_f(row[F + f]);
+  out[i] = from_f<T>((act == 0 ? siluf_(g) : gelu_tanhf_(g)) * u);
+}
+
+// x[r, c] += ls1[c] * a[r, c] + ls2[c] * (b[r, c] + b2[r, c]): the residual update of a block whose mixer and
+// feed-forward read the same normed input, each branch with a learned scale per channel.  b, b2 and the scales are
+// optional (absent scale = 1); x is the fp32 residual.
+template <typename T>
+__global__ void scaled_branches_kernel(float* __restrict__ x, long long x_stride, const T* __restrict__ a,
+                                       long long a_stride, const T* __restrict__ ls1, const T* __restrict__ b,
+                                       long long b_stride, const T* __restrict__ b2, long long b2_stride,
+                                       const T* __restrict__ ls2, int C) {
+  size_t r = blockIdx.x;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float y = to_f(a[r * a_stride + c]) * (ls1 ? to_f(ls1[c]) : 1.f);
+    if (b) {
+      float f = to_f(b[r * b_stride + c]);
+      if (b2) f += to_f(b2[r * b2_stride + c]);
+      y += f * (ls2 ? to_f(ls2[c]) : 1.f);
+    }
+    x[r * x_stride + c] += y;
   }
 }
 
@@ -1311,24 +1418,30 @@ extern "C" {
 
 int hyb_window_append(void* q, long long q_stride, const void* k, long long k_stride, const void* v, long long v_stride,
                       const float* inv_freq, void* cache, long long slot_stride, const int* meta, const int* tok_seq,
-                      int N, int H, int G, int D, int V, int nrot, float eps, int dt, cudaStream_t st) {
+                      int N, int H, int G, int D, int V, int nrot, float eps, const void* qw, const void* kw,
+                      const void* v_first, long long vf_stride, const void* lam, int dt, cudaStream_t st) {
   if (N == 0) return 0;
   if (D > 32 * WA_MAXD || nrot > D || (nrot & 1) || (nrot > 0 && !inv_freq)) return -3;
+  if (lam && !v_first) return -2;
   HYB_DISPATCH(dt,
                (window_append_kernel<bf16><<<N, 128, 0, st>>>((bf16*)q, q_stride, (const bf16*)k, k_stride, (const bf16*)v,
                                                               v_stride, inv_freq, (bf16*)cache, slot_stride, meta, tok_seq,
-                                                              H, G, D, V, nrot, eps)),
+                                                              H, G, D, V, nrot, eps, (const bf16*)qw, (const bf16*)kw,
+                                                              (const bf16*)v_first, vf_stride, (const bf16*)lam)),
                (window_append_kernel<float><<<N, 128, 0, st>>>((float*)q, q_stride, (const float*)k, k_stride,
                                                                (const float*)v, v_stride, inv_freq, (float*)cache,
-                                                               slot_stride, meta, tok_seq, H, G, D, V, nrot, eps)));
+                                                               slot_stride, meta, tok_seq, H, G, D, V, nrot, eps,
+                                                               (const float*)qw, (const float*)kw, (const float*)v_first,
+                                                               vf_stride, (const float*)lam)));
   return (int)cudaGetLastError();
 }
 
 int hyb_window_attn(const void* q, long long q_stride, const void* gate, long long g_stride, const void* cache,
                     long long slot_stride, const int* meta, const int* tok_seq, void* out, int N, int H, int G, int D,
-                    int V, float scale, int window, int nsplit, float* part_acc, float* part_ml, int dt,
-                    cudaStream_t st) {
+                    int V, float scale, int window, int nsplit, float* part_acc, float* part_ml, int mask_kind, int sink,
+                    int gate_mode, int dt, cudaStream_t st) {
   if (N == 0) return 0;
+  if (mask_kind < 0 || mask_kind > 1 || (mask_kind == 1 && window < 1) || gate_mode < 0 || gate_mode > 2) return -3;
   int rep = G > 0 ? H / G : 0;
   if (rep < 1 || rep * G != H || rep > 32 || V > 32 * WT_MAXV) return -3;
   if (nsplit < 1 || (nsplit > 1 && (!part_acc || !part_ml))) return -2;
@@ -1340,16 +1453,18 @@ int hyb_window_attn(const void* q, long long q_stride, const void* gate, long lo
     if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(window_attn_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
     window_attn_kernel<bf16><<<grid, 32 * rep, smem, st>>>((const bf16*)q, q_stride, (const bf16*)gate, g_stride,
                                                            (const bf16*)cache, slot_stride, meta, tok_seq, (bf16*)out, H,
-                                                           G, D, V, scale, window, nsplit, part_acc, part_ml);
+                                                           G, D, V, scale, window, nsplit, part_acc, part_ml, mask_kind, sink,
+                                                           gate_mode);
     if (nsplit > 1)
-      window_combine_kernel<bf16><<<cgrid, 64, 0, st>>>(part_acc, part_ml, (const bf16*)gate, g_stride, (bf16*)out, N, H, V, nsplit);
+      window_combine_kernel<bf16><<<cgrid, 64, 0, st>>>(part_acc, part_ml, (const bf16*)gate, g_stride, (bf16*)out, N, H, V, nsplit, sink, gate_mode);
   } else {
     if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(window_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
     window_attn_kernel<float><<<grid, 32 * rep, smem, st>>>((const float*)q, q_stride, (const float*)gate, g_stride,
                                                             (const float*)cache, slot_stride, meta, tok_seq, (float*)out,
-                                                            H, G, D, V, scale, window, nsplit, part_acc, part_ml);
+                                                            H, G, D, V, scale, window, nsplit, part_acc, part_ml, mask_kind, sink,
+                                                            gate_mode);
     if (nsplit > 1)
-      window_combine_kernel<float><<<cgrid, 64, 0, st>>>(part_acc, part_ml, (const float*)gate, g_stride, (float*)out, N, H, V, nsplit);
+      window_combine_kernel<float><<<cgrid, 64, 0, st>>>(part_acc, part_ml, (const float*)gate, g_stride, (float*)out, N, H, V, nsplit, sink, gate_mode);
   }
   return (int)cudaGetLastError();
 }
@@ -1377,10 +1492,10 @@ int hyb_token_side_gate(const void* z, long long z_stride, const void* table, lo
   return (int)cudaGetLastError();
 }
 
-int hyb_router_topk(const float* z, int* idx, float* wt, int N, int E, int top, cudaStream_t st) {
+int hyb_router_topk(const float* z, int* idx, float* wt, int N, int E, int top, int mode, cudaStream_t st) {
   if (N == 0) return 0;
-  if (top < 1 || top > E) return -3;
-  router_topk_kernel<<<(N + 63) / 64, 64, 0, st>>>(z, idx, wt, N, E, top);
+  if (top < 1 || top > E || mode < 0 || mode > 1) return -3;
+  router_topk_kernel<<<(N + 63) / 64, 64, 0, st>>>(z, idx, wt, N, E, top, mode);
   return (int)cudaGetLastError();
 }
 
@@ -1406,23 +1521,30 @@ static int launch_moe_pairs(const void* x, long long x_stride, const int* idx, c
 
 extern "C" {
 
-// act [N*top, ff] fp32 = squared-ReLU of the chosen experts' up projections of the score-weighted token.
+// act [N*top, ff] fp32.  gated 0: squared-ReLU of the chosen experts' up projections of the score-weighted token
+// (up [E, ff, C]).  gated 1: silu(gate x) * (up x) of the token as it is (up [E, 2 ff, C], gate rows first).
 int hyb_moe_up(const void* h, long long h_stride, const int* idx, const float* wt, const void* up, float* act, int N,
-               int top, int C, int ff, int E, int dt, cudaStream_t st) {
+               int top, int C, int ff, int E, int gated, int dt, cudaStream_t st) {
   if (N == 0) return 0;
+  if (gated) {
+    if (dt == 0) return launch_moe_pairs<bf16, 2>(h, h_stride, idx, wt, up, act, N * top, top, C, ff, E, st);
+    return launch_moe_pairs<float, 2>(h, h_stride, idx, wt, up, act, N * top, top, C, ff, E, st);
+  }
+  if (!wt) return -2;
   if (dt == 0) return launch_moe_pairs<bf16, 0>(h, h_stride, idx, wt, up, act, N * top, top, C, ff, E, st);
   return launch_moe_pairs<float, 0>(h, h_stride, idx, wt, up, act, N * top, top, C, ff, E, st);
 }
 
-// out [N, C] = sum over a token's choices of the expert's down projection of act; ypair [N*top, C] fp32 is scratch.
-int hyb_moe_down(const float* act, const int* idx, const void* down, float* ypair, void* out, int N, int top, int C,
-                 int ff, int E, int dt, cudaStream_t st) {
+// out [N, C] = sum over a token's choices of the expert's down projection of act, each times wt[choice] when wt is
+// given; ypair [N*top, C] fp32 is scratch.
+int hyb_moe_down(const float* act, const int* idx, const float* wt, const void* down, float* ypair, void* out, int N,
+                 int top, int C, int ff, int E, int dt, cudaStream_t st) {
   if (N == 0) return 0;
   int rc = dt == 0 ? launch_moe_pairs<bf16, 1>(act, ff, idx, nullptr, down, ypair, N * top, top, ff, C, E, st)
                    : launch_moe_pairs<float, 1>(act, ff, idx, nullptr, down, ypair, N * top, top, ff, C, E, st);
   if (rc) return rc;
-  HYB_DISPATCH(dt, (moe_sum_kernel<bf16><<<N, 256, 0, st>>>(ypair, (bf16*)out, top, C)),
-               (moe_sum_kernel<float><<<N, 256, 0, st>>>(ypair, (float*)out, top, C)));
+  HYB_DISPATCH(dt, (moe_sum_kernel<bf16><<<N, 256, 0, st>>>(ypair, wt, (bf16*)out, top, C)),
+               (moe_sum_kernel<float><<<N, 256, 0, st>>>(ypair, wt, (float*)out, top, C)));
   return (int)cudaGetLastError();
 }
 
@@ -1435,10 +1557,37 @@ int hyb_gather_scale_rows(const void* h, long long h_stride, const int* rows, co
   return (int)cudaGetLastError();
 }
 
-int hyb_combine_rows(const void* y, const int* where, void* out, int n, int top, int C, int dt, cudaStream_t st) {
+int hyb_combine_rows(const void* y, const int* where, const float* wt, void* out, int n, int top, int C, int dt,
+                     cudaStream_t st) {
   if (n == 0) return 0;
-  HYB_DISPATCH(dt, (combine_rows_kernel<bf16><<<n, 256, 0, st>>>((const bf16*)y, where, (bf16*)out, top, C)),
-               (combine_rows_kernel<float><<<n, 256, 0, st>>>((const float*)y, where, (float*)out, top, C)));
+  HYB_DISPATCH(dt, (combine_rows_kernel<bf16><<<n, 256, 0, st>>>((const bf16*)y, where, wt, (bf16*)out, top, C)),
+               (combine_rows_kernel<float><<<n, 256, 0, st>>>((const float*)y, where, wt, (float*)out, top, C)));
+  return (int)cudaGetLastError();
+}
+
+int hyb_act_mul_rows(const void* in, long long in_stride, void* out, long long rows, int F, int act, int dt,
+                     cudaStream_t st) {
+  long long total = rows * F;
+  if (total == 0) return 0;
+  if (act < 0 || act > 1) return -3;
+  unsigned blocks = (unsigned)((total + 255) / 256);
+  HYB_DISPATCH(dt, (act_mul_rows_kernel<bf16><<<blocks, 256, 0, st>>>((const bf16*)in, in_stride, (bf16*)out, F, act, total)),
+               (act_mul_rows_kernel<float><<<blocks, 256, 0, st>>>((const float*)in, in_stride, (float*)out, F, act, total)));
+  return (int)cudaGetLastError();
+}
+
+int hyb_scaled_branches(float* x, long long x_stride, const void* a, long long a_stride, const void* ls1, const void* b,
+                        long long b_stride, const void* b2, long long b2_stride, const void* ls2, int rows, int C, int dt,
+                        cudaStream_t st) {
+  if (rows == 0) return 0;
+  if (b2 && !b) return -2;
+  HYB_DISPATCH(dt,
+               (scaled_branches_kernel<bf16><<<rows, 256, 0, st>>>(x, x_stride, (const bf16*)a, a_stride, (const bf16*)ls1,
+                                                                   (const bf16*)b, b_stride, (const bf16*)b2, b2_stride,
+                                                                   (const bf16*)ls2, C)),
+               (scaled_branches_kernel<float><<<rows, 256, 0, st>>>(x, x_stride, (const float*)a, a_stride,
+                                                                    (const float*)ls1, (const float*)b, b_stride,
+                                                                    (const float*)b2, b2_stride, (const float*)ls2, C)));
   return (int)cudaGetLastError();
 }
 

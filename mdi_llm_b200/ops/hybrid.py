@@ -18,8 +18,8 @@ from __future__ import annotations
 import ctypes
 import math
 from ctypes import c_float, c_int, c_longlong, c_void_p
-from dataclasses import dataclass
-from typing import List, Optional, Sequence, Tuple
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 import torch.nn.functional as F
@@ -29,7 +29,7 @@ from . import build as _build
 __all__ = ["BatchPlan", "HybridOpsError", "lib", "embed_rows", "cast_into", "norm_rows", "norm_accumulate", "gelu_",
            "headmajor_gate", "softcap", "latent_append", "latent_attn", "causal_softmax", "matmul_f32", "conv_silu", "gated_recurrence", "linear",
            "rotary_inv_freq", "scaled_inv_freq", "linear_f32", "grouped_linear", "window_append", "window_attn", "head_gate", "relu2_",
-           "token_side_gate", "router_topk", "moe_gemv", "gather_scale_rows", "combine_rows"]
+           "token_side_gate", "router_topk", "moe_gemv", "gather_scale_rows", "combine_rows", "act_mul", "scaled_branches"]
 
 
 class HybridOpsError(RuntimeError):
@@ -59,24 +59,26 @@ def lib() -> ctypes.CDLL:
     vp, i32, i64, f32 = c_void_p, c_int, c_longlong, c_float
     h.hyb_error_string.restype = ctypes.c_char_p
     h.hyb_error_string.argtypes = [i32]
-    h.hyb_embed_rows.argtypes = [vp, vp, vp, i32, i32, i32, vp]
+    h.hyb_embed_rows.argtypes = [vp, vp, vp, i32, i32, vp, vp, vp, i32, vp]
     h.hyb_cast_rows.argtypes = [vp, i64, i32, vp, i64, i32, i32, i32, vp]
-    h.hyb_norm_rows.argtypes = [vp, i64, i32, vp, vp, i32, vp, i64, i32, i32, i32, f32, i32, i32, f32, vp]
+    h.hyb_norm_rows.argtypes = [vp, i64, i32, vp, vp, i32, vp, i64, i32, i32, i32, f32, i32, i32, f32, f32, vp]
     h.hyb_gelu_rows.argtypes = [vp, i64, i32, i32, vp]
-    h.hyb_window_append.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp]
-    h.hyb_window_attn.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, i32, vp, vp, i32, vp]
+    h.hyb_window_append.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp, vp, i64, vp, i32, vp]
+    h.hyb_window_attn.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, i32, vp, vp, i32, i32, i32, i32, vp]
     h.hyb_head_gate.argtypes = [vp, vp, i64, vp, i32, i32, i32, i32, vp]
     h.hyb_token_side_gate.argtypes = [vp, i64, vp, i64, i32, vp, vp, i32, i32, i32, vp]
-    h.hyb_router_topk.argtypes = [vp, vp, vp, i32, i32, i32, vp]
-    h.hyb_moe_up.argtypes = [vp, i64, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]
-    h.hyb_moe_down.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]
+    h.hyb_router_topk.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
+    h.hyb_moe_up.argtypes = [vp, i64, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp]
+    h.hyb_moe_down.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]
     h.hyb_gather_scale_rows.argtypes = [vp, i64, vp, vp, vp, i32, i32, i32, vp]
-    h.hyb_combine_rows.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
+    h.hyb_combine_rows.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, vp]
+    h.hyb_act_mul_rows.argtypes = [vp, i64, vp, i64, i32, i32, i32, vp]
+    h.hyb_scaled_branches.argtypes = [vp, i64, vp, i64, vp, vp, i64, vp, i64, vp, i32, i32, i32, vp]
     h.hyb_headmajor_gate.argtypes = [vp, vp, i64, vp, i32, i32, i32, i32, vp]
     h.hyb_softcap.argtypes = [vp, vp, i64, f32, i32, vp]
     h.hyb_latent_append.argtypes = [vp, i64, vp, i64, vp, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp]
     h.hyb_latent_attn.argtypes = [vp, vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp, vp, i32, vp]
-    h.hyb_causal_softmax.argtypes = [vp, vp, i64, i32, i32, i32, f32, i32, i32, i32, vp]
+    h.hyb_causal_softmax.argtypes = [vp, vp, i64, i32, i32, i32, f32, i32, i32, i32, i32, vp]
     h.hyb_conv_silu.argtypes = [vp, i64, vp, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, vp]
     h.hyb_gated_recurrence.argtypes = [ctypes.POINTER(_RecArgs), i32, i32, i32, i32, vp, vp, vp, vp]
     _lib = h
@@ -110,13 +112,17 @@ def _rows(t: torch.Tensor) -> Tuple[int, int]:
 
 @dataclass
 class BatchPlan:
-    """One step's packed batch: ``seqs[i] = (first row, tokens, slot, position of the first token)``."""
+    """One step's packed batch: ``seqs[i] = (first row, tokens, slot, position of the first token)``.
+
+    ``shared`` is the step's scratch between layers: what one layer computes for this step's tokens and a later layer
+    reads (the values of the first value-mixing attention layer).  The model clears it when a step starts."""
 
     seqs: List[Tuple[int, int, int, int]]
     n_tokens: int
     meta: torch.Tensor      # int32 [n_seq, 4] on the compute device
     tok_seq: torch.Tensor   # int32 [n_tokens]: sequence index of every row
     positions: torch.Tensor  # int64 [n_tokens]
+    shared: Dict[str, torch.Tensor] = field(default_factory=dict)
 
     @classmethod
     def make(cls, lengths: Sequence[int], slots: Sequence[int], starts: Sequence[int], device: torch.device) -> "BatchPlan":
@@ -159,11 +165,11 @@ def scaled_inv_freq(dims: int, base: float, scaling: Optional[dict], device: tor
     return f.to(torch.float32).to(device)
 
 
-def linear_f32(x: torch.Tensor, w32: torch.Tensor) -> torch.Tensor:
-    """``x @ w32.T`` in fp32 (routers): the input may be the activation type, the product and the result are fp32."""
+def linear_f32(x: torch.Tensor, w32: torch.Tensor, b32: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ w32.T (+ b32)`` in fp32 (routers): the input may be the activation type, the product and the result are fp32."""
     if x.is_cuda and torch.backends.cuda.matmul.allow_tf32:
         raise HybridOpsError("TF32 matrix products are on; router logits are fp32")
-    return F.linear(x.float(), w32)
+    return F.linear(x.float(), w32, b32)
 
 
 def grouped_linear(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor) -> torch.Tensor:
@@ -182,23 +188,30 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor) -> to
     return out
 
 
-def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """``x @ w.T`` in the activation type with fp32 accumulation."""
+def linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ w.T (+ b)`` in the activation type with fp32 accumulation."""
     if x.is_cuda and x.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
         raise HybridOpsError("TF32 matrix products are on; fp32 mode needs torch.backends.cuda.matmul.allow_tf32 = False")
-    return F.linear(x, w)
+    return F.linear(x, w, b)
 
 
 # ---------------------------------------------------------------------------------------------------------
 # rows
 # ---------------------------------------------------------------------------------------------------------
-def embed_rows(table: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
-    """fp32 rows of ``table`` for int32 ``tokens [N]``."""
+def embed_rows(table: torch.Tensor, tokens: torch.Tensor, pos_table: Optional[torch.Tensor] = None,
+               plan: Optional["BatchPlan"] = None) -> torch.Tensor:
+    """fp32 rows of ``table`` for int32 ``tokens [N]``; with ``pos_table [positions, width]`` the learned vector of each
+    token's position in its sequence (from ``plan``) is added, unscaled, in fp32."""
     if not table.is_cuda:
-        return table[tokens.long()].float()
+        x = table[tokens.long()].float()
+        return x if pos_table is None else x + pos_table[plan.positions].float()
     x = torch.empty(tokens.numel(), table.size(1), device=table.device, dtype=torch.float32)
+    if pos_table is not None and (pos_table.dtype != table.dtype or pos_table.size(1) != table.size(1) or not pos_table.is_contiguous()):
+        raise HybridOpsError("the position table has the embedding table's type and width")
     _check(lib().hyb_embed_rows(table.data_ptr(), tokens.data_ptr(), x.data_ptr(), tokens.numel(), table.size(1),
-                                _dt(table), _st()), "embed_rows")
+                                None if pos_table is None else pos_table.data_ptr(),
+                                None if pos_table is None else plan.meta.data_ptr(),
+                                None if pos_table is None else plan.tok_seq.data_ptr(), _dt(table), _st()), "embed_rows")
     return x
 
 
@@ -213,7 +226,8 @@ def cast_into(src: torch.Tensor, dst: torch.Tensor) -> None:
     _check(lib().hyb_cast_rows(src.data_ptr(), ss, _dt(src), dst.data_ptr(), ds, _dt(dst), src.size(0), n, _st()), "cast_rows")
 
 
-def _norm_torch(x: torch.Tensor, w: Optional[torch.Tensor], b: Optional[torch.Tensor], eps: float, kind: str) -> torch.Tensor:
+def _norm_torch(x: torch.Tensor, w: Optional[torch.Tensor], b: Optional[torch.Tensor], eps: float, kind: str,
+                w_offset: float = 0.0) -> torch.Tensor:
     xf = x.float()
     if kind == "none":
         return xf
@@ -221,23 +235,24 @@ def _norm_torch(x: torch.Tensor, w: Optional[torch.Tensor], b: Optional[torch.Te
         xf = xf - xf.mean(-1, keepdim=True)
     y = xf / torch.sqrt((xf * xf).mean(-1, keepdim=True) + eps)
     if w is not None:
-        y = y * w.float()
+        y = y * (w.float() + w_offset if w_offset else w.float())
     if b is not None:
         y = y + b.float()
     return y
 
 
 def norm_rows(x: torch.Tensor, w: Optional[torch.Tensor], b: Optional[torch.Tensor], eps: float, kind: str,
-              out_dtype: torch.dtype) -> torch.Tensor:
-    """Layer norm (``kind="layer"``: weight and bias) or RMS norm (``kind="rms"``) of every row, statistics in fp32."""
+              out_dtype: torch.dtype, w_offset: float = 0.0) -> torch.Tensor:
+    """Layer norm (``kind="layer"``: weight and bias) or RMS norm (``kind="rms"``) of every row, statistics in fp32.
+    The weight applied is ``w_offset + w`` (``w_offset = 1``: a weight stored as its deviation from one), summed in fp32."""
     if not x.is_cuda:
-        return _norm_torch(x, w, b, eps, kind).to(out_dtype)
+        return _norm_torch(x, w, b, eps, kind, w_offset).to(out_dtype)
     xs, n = _rows(x)
     out = torch.empty(x.size(0), n, device=x.device, dtype=out_dtype)
     ref = w if w is not None else x
     _check(lib().hyb_norm_rows(x.data_ptr(), xs, _dt(x), None if w is None else w.data_ptr(),
                                None if b is None else b.data_ptr(), _dt(ref), out.data_ptr(), n, _dt(out), x.size(0), n,
-                               eps, _NORM_KINDS[kind], 0, 1.0, _st()), "norm_rows")
+                               eps, _NORM_KINDS[kind], 0, 1.0, float(w_offset), _st()), "norm_rows")
     return out
 
 
@@ -257,7 +272,7 @@ def norm_accumulate(resid: torch.Tensor, y: torch.Tensor, w: Optional[torch.Tens
     ref = w if w is not None else y
     _check(lib().hyb_norm_rows(y.data_ptr(), ys, _dt(y), None if w is None else w.data_ptr(),
                                None if b is None else b.data_ptr(), _dt(ref), resid.data_ptr(), resid.stride(0), 1,
-                               y.size(0), n, eps, _NORM_KINDS[kind], 1, float(scale), _st()), "norm_accumulate")
+                               y.size(0), n, eps, _NORM_KINDS[kind], 1, float(scale), 0.0, _st()), "norm_accumulate")
 
 
 def gelu_(x: torch.Tensor) -> torch.Tensor:
@@ -402,10 +417,11 @@ def latent_attn(qlat: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, plan: 
 
 
 def causal_softmax(scores: torch.Tensor, first_pos: int, scale: float, out_dtype: torch.dtype, window: int = 0,
-                   key0: int = 0) -> torch.Tensor:
+                   key0: int = 0, sink: bool = False) -> torch.Tensor:
     """``softmax(scale * scores)`` over the visible keys of fp32 ``scores [heads, rows, keys]``: row ``i`` is position
     ``first_pos + i``, column ``j`` is position ``key0 + j``; a key is visible when it is not later than the row and,
-    with ``window > 0``, fewer than ``window`` positions back.  Hidden keys get probability 0.  Result in ``out_dtype``."""
+    with ``window > 0``, fewer than ``window`` positions back.  Hidden keys get probability 0.  Result in ``out_dtype``.
+    ``sink``: the denominator gains one slot of score zero that has no value, ``p_j = e^{s_j} / (1 + sum_k e^{s_k})``."""
     Hh, n, keys = scores.shape
     if not scores.is_cuda:
         j = key0 + torch.arange(keys)
@@ -413,12 +429,15 @@ def causal_softmax(scores: torch.Tensor, first_pos: int, scale: float, out_dtype
         hidden = j[None, None, :] > pi
         if window > 0:
             hidden = hidden | (pi - j[None, None, :] >= window)
-        return torch.softmax((scores.float() * scale).masked_fill(hidden, float("-inf")), -1).to(out_dtype)
+        sc = (scores.float() * scale).masked_fill(hidden, float("-inf"))
+        if sink:
+            sc = torch.cat((sc, sc.new_zeros(Hh, n, 1)), -1)
+        return torch.softmax(sc, -1)[..., :keys].to(out_dtype)
     if scores.dtype != torch.float32 or not scores.is_contiguous():
         raise HybridOpsError("scores are dense fp32")
     p = torch.empty(Hh, n, keys, device=scores.device, dtype=out_dtype)
     _check(lib().hyb_causal_softmax(scores.data_ptr(), p.data_ptr(), Hh * n, n, keys, int(first_pos), float(scale),
-                                    int(window), int(key0), _dt(p), _st()), "causal_softmax")
+                                    int(window), int(key0), int(bool(sink)), _dt(p), _st()), "causal_softmax")
     return p
 
 
@@ -426,14 +445,19 @@ def causal_softmax(scores: torch.Tensor, first_pos: int, scale: float, out_dtype
 # windowed grouped-query attention with a per-slot key/value cache
 # ---------------------------------------------------------------------------------------------------------
 def window_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, inv_freq: Optional[torch.Tensor], cache: torch.Tensor,
-                  plan: BatchPlan, H: int, G: int, D: int, V: int, nrot: int, eps: float) -> None:
+                  plan: BatchPlan, H: int, G: int, D: int, V: int, nrot: int, eps: float,
+                  qw: Optional[torch.Tensor] = None, kw: Optional[torch.Tensor] = None,
+                  v_first: Optional[torch.Tensor] = None, lam: Optional[torch.Tensor] = None) -> None:
     """Per token: rotate the first ``nrot`` entries of every query and key head (entry ``2i`` paired with ``2i+1``,
     angle ``pos * inv_freq[i]``), divide each head by its root mean square over ``D`` (``eps`` inside the root), keep
-    the queries in place and write ``[keys | values]`` to ``cache[slot, pos]`` (row = ``G*D`` keys then ``G*V`` values)."""
+    the queries in place and write ``[keys | values]`` to ``cache[slot, pos]`` (row = ``G*D`` keys then ``G*V`` values).
+    ``qw`` / ``kw`` (``[D]``, shared by the heads) multiply the normalised queries / keys.  With ``lam`` (a one-element
+    tensor) the values written are ``(1 - lam) v + lam v_first``, evaluated in fp32 (``v_first [N, G*V]``: the values
+    another layer computed for the same tokens)."""
     if not q.is_cuda:
         N = q.size(0)
 
-        def prep(x: torch.Tensor, heads: int) -> torch.Tensor:
+        def prep(x: torch.Tensor, heads: int, w: Optional[torch.Tensor]) -> torch.Tensor:
             xf = x.float().reshape(N, heads, D).clone()
             if nrot:
                 ang = plan.positions.float()[:, None] * inv_freq[None, :]
@@ -442,25 +466,49 @@ def window_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, inv_freq: O
                 xf[..., 0:nrot:2] = u * c - w_ * s_
                 xf[..., 1:nrot:2] = w_ * c + u * s_
             xf = xf / torch.sqrt((xf * xf).mean(-1, keepdim=True) + eps)
+            if w is not None:
+                xf = xf * w.float()
             return xf.reshape(N, heads * D).to(x.dtype)
 
-        q.copy_(prep(q, H))
-        kk = prep(k, G)
+        q.copy_(prep(q, H, qw))
+        kk = prep(k, G, kw)
+        vv = v if lam is None else ((1.0 - lam.float()) * v.float() + lam.float() * v_first.float()).to(v.dtype)
         for r0, n, slot, p0 in plan.seqs:
             cache[slot, p0:p0 + n, :G * D] = kk[r0:r0 + n]
-            cache[slot, p0:p0 + n, G * D:] = v[r0:r0 + n]
+            cache[slot, p0:p0 + n, G * D:] = vv[r0:r0 + n]
         return
+    for w in (qw, kw, lam):
+        if w is not None and (w.dtype != q.dtype or not w.is_contiguous()):
+            raise HybridOpsError("norm weights and the mixing factor have the activation type")
     _check(lib().hyb_window_append(q.data_ptr(), _rows(q)[0], k.data_ptr(), _rows(k)[0], v.data_ptr(), _rows(v)[0],
                                    None if inv_freq is None else inv_freq.data_ptr(), cache.data_ptr(), cache.stride(0),
                                    plan.meta.data_ptr(), plan.tok_seq.data_ptr(), q.size(0), H, G, D, V, int(nrot),
-                                   float(eps), _dt(q), _st()), "window_append")
+                                   float(eps), None if qw is None else qw.data_ptr(), None if kw is None else kw.data_ptr(),
+                                   None if lam is None else v_first.data_ptr(), 0 if lam is None else _rows(v_first)[0],
+                                   None if lam is None else lam.data_ptr(), _dt(q), _st()), "window_append")
+
+
+_MASK_KINDS = {"window": 0, "chunk": 1}
+
+
+def visible_from(pos: torch.Tensor, window: int, mask: str) -> torch.Tensor:
+    """First visible position for queries at ``pos``: ``window`` positions back (``mask="window"``; 0 = unlimited), or
+    the start of the query's own block of ``window`` positions counted from 0 (``mask="chunk"``)."""
+    if window <= 0:
+        return torch.zeros_like(pos)
+    if mask == "chunk":
+        return torch.div(pos, window, rounding_mode="floor") * window
+    return torch.clamp(pos - window + 1, min=0)
 
 
 def window_attn(q: torch.Tensor, g: Optional[torch.Tensor], cache: torch.Tensor, plan: BatchPlan, H: int, G: int, D: int,
-                V: int, scale: float, window: int, split: int = 0) -> torch.Tensor:
+                V: int, scale: float, window: int, split: int = 0, mask: str = "window", sink: bool = False) -> torch.Tensor:
     """Softmax attention of every token over the cached keys of its slot that are not later than it and (``window > 0``)
     fewer than ``window`` positions back; query head ``h`` reads key/value head ``h // (H/G)``.  Each head's output is
-    multiplied by ``sigmoid(g[token, h])`` when ``g`` is given.  Returns ``[N, H*V]``.  The form for one-token steps and
+    multiplied by ``sigmoid(g[token, h])`` when ``g [N, H]`` is given, or channel by channel by ``sigmoid(g)`` for
+    ``g [N, H*V]``.  ``mask="chunk"``: a token sees the earlier keys of its own block of ``window`` positions (blocks
+    counted from position 0 of the sequence) instead of the last ``window``.  ``sink``: the softmax denominator gains
+    one slot of score zero without a value.  Returns ``[N, H*V]``.  The form for one-token steps and
     short portions: one block per token and key/value head, the cache tile shared by the group's query heads.
     ``split`` (CUDA): key shares per token, 0 = chosen from the batch shape and the window alone, so that a captured
     step stays valid while contexts grow."""
@@ -476,14 +524,20 @@ def window_attn(q: torch.Tensor, g: Optional[torch.Tensor], cache: torch.Tensor,
             s = torch.einsum("nhd,khd->hnk", qq, kk) * scale
             pi = (p0 + torch.arange(n))[None, :, None]
             j = torch.arange(p0 + n)[None, None, :]
-            hid = j > pi
-            if window > 0:
-                hid = hid | (pi - j >= window)
-            o = torch.einsum("hnk,khv->nhv", torch.softmax(s.masked_fill(hid, float("-inf")), -1), vv)
-            if g is not None:
+            hid = (j > pi) | (j < visible_from(pi, window, mask))
+            s = s.masked_fill(hid, float("-inf"))
+            if sink:
+                s = torch.cat((s, s.new_zeros(H, n, 1)), -1)
+            o = torch.einsum("hnk,khv->nhv", torch.softmax(s, -1)[..., :p0 + n], vv)
+            if g is not None and g.size(1) == H * V and V != 1:
+                o = o * torch.sigmoid(g[r0:r0 + n].float()).view(n, H, V)
+            elif g is not None:
                 o = o * torch.sigmoid(g[r0:r0 + n].float())[:, :, None]
             out[r0:r0 + n] = o.reshape(n, H * V).to(q.dtype)
         return out
+    if g is not None and g.size(1) not in (H, H * V):
+        raise HybridOpsError("the gate has one column per head or per output channel")
+    gate_mode = 0 if g is None else (1 if g.size(1) == H else 2)
     out = torch.empty(N, H * V, device=q.device, dtype=q.dtype)
     blocks = N * G
     tiles = (window + 31) // 32 if window > 0 else 16
@@ -496,18 +550,25 @@ def window_attn(q: torch.Tensor, g: Optional[torch.Tensor], cache: torch.Tensor,
                                  0 if g is None else _rows(g)[0], cache.data_ptr(), cache.stride(0), plan.meta.data_ptr(),
                                  plan.tok_seq.data_ptr(), out.data_ptr(), N, H, G, D, V, float(scale), int(window), nsplit,
                                  None if pa is None else pa.data_ptr(), None if pm is None else pm.data_ptr(),
-                                 _dt(q), _st()), "window_attn")
+                                 _MASK_KINDS[mask], int(bool(sink)), gate_mode, _dt(q), _st()), "window_attn")
     return out
 
 
 # ---------------------------------------------------------------------------------------------------------
 # mixture of experts: sigmoid router, top-k choice, experts applied to the weighted input
 # ---------------------------------------------------------------------------------------------------------
-def router_topk(z: torch.Tensor, top: int) -> Tuple[torch.Tensor, torch.Tensor]:
-    """From fp32 router logits ``z [N, E]``: the ``top`` experts with the largest ``sigmoid(z)`` per token (ties go to
-    the lower index) as int32 ``[N, top]`` and their scores as fp32 ``[N, top]`` (not renormalised)."""
+_ROUTER_MODES = {"sigmoid": 0, "softmax": 1}
+
+
+def router_topk(z: torch.Tensor, top: int, mode: str = "sigmoid") -> Tuple[torch.Tensor, torch.Tensor]:
+    """From fp32 router logits ``z [N, E]``: the ``top`` experts with the largest logits per token (ties go to the lower
+    index) as int32 ``[N, top]`` and their scores as fp32 ``[N, top]``: ``sigmoid(z)`` of each, not renormalised
+    (``mode="sigmoid"``), or the softmax over the chosen logits only (``mode="softmax"``)."""
     N, E = z.shape
     if not z.is_cuda:
+        if mode == "softmax":
+            idx = torch.argsort(-z.float(), dim=-1, stable=True)[:, :top]
+            return idx.to(torch.int32), torch.softmax(torch.gather(z.float(), 1, idx), -1)
         s = torch.sigmoid(z.float())
         idx = torch.argsort(-s, dim=-1, stable=True)[:, :top]
         return idx.to(torch.int32), torch.gather(s, 1, idx)
@@ -515,22 +576,32 @@ def router_topk(z: torch.Tensor, top: int) -> Tuple[torch.Tensor, torch.Tensor]:
         raise HybridOpsError("router logits are dense fp32")
     idx = torch.empty(N, top, device=z.device, dtype=torch.int32)
     wt = torch.empty(N, top, device=z.device, dtype=torch.float32)
-    _check(lib().hyb_router_topk(z.data_ptr(), idx.data_ptr(), wt.data_ptr(), N, E, int(top), _st()), "router_topk")
+    _check(lib().hyb_router_topk(z.data_ptr(), idx.data_ptr(), wt.data_ptr(), N, E, int(top), _ROUTER_MODES[mode], _st()),
+           "router_topk")
     return idx, wt
 
 
-def moe_gemv(h: torch.Tensor, idx: torch.Tensor, wt: torch.Tensor, up: torch.Tensor, down: torch.Tensor) -> torch.Tensor:
-    """``sum_k down[e_k] relu(up[e_k] (w_k h))^2`` per token, experts read by index (``up [E, ff, C]``, ``down [E, C, ff]``).
-    The form for few tokens: weight-streaming kernels in which one block serves every token that chose its expert
-    (an expert's weights are read once per step), no sorting and no host synchronisation."""
+def moe_gemv(h: torch.Tensor, idx: torch.Tensor, wt: torch.Tensor, up: torch.Tensor, down: torch.Tensor,
+             gated: bool = False) -> torch.Tensor:
+    """Experts read by index, per token.  ``gated=False``: ``sum_k down[e_k] relu(up[e_k] (w_k h))^2`` (``up [E, ff, C]``:
+    the score scales the expert's input).  ``gated=True``: ``sum_k w_k down[e_k] (silu(G h) * (U h))`` with
+    ``up [E, 2 ff, C]`` holding an expert's gate rows ``G`` and then its up rows ``U`` (the score weighs the expert's
+    output).  ``down [E, C, ff]``.  The form for few tokens: weight-streaming kernels in which one block serves every
+    token that chose its expert (an expert's weights are read once per step), no sorting and no host synchronisation."""
     N, C = h.shape
     E, ff, _ = up.shape
+    if gated:
+        ff //= 2
     top = idx.size(1)
     if not h.is_cuda:
         out = torch.zeros(N, C)
         for t in range(N):
             for k in range(top):
                 e = int(idx[t, k])
+                if gated:
+                    gu = F.linear(h[t], up[e]).float()
+                    out[t] += wt[t, k] * F.linear((F.silu(gu[:ff]) * gu[ff:]).to(h.dtype), down[e]).float()
+                    continue
                 xin = (wt[t, k] * h[t].float()).to(h.dtype)
                 a = torch.relu(F.linear(xin, up[e]).float()).square().to(h.dtype)
                 out[t] += F.linear(a, down[e]).float()
@@ -540,32 +611,80 @@ def moe_gemv(h: torch.Tensor, idx: torch.Tensor, wt: torch.Tensor, up: torch.Ten
     ypair = torch.empty(N, top, C, device=h.device, dtype=torch.float32)
     out = torch.empty(N, C, device=h.device, dtype=h.dtype)
     _check(lib().hyb_moe_up(h.data_ptr(), _rows(h)[0], idx.data_ptr(), wt.data_ptr(), up.data_ptr(), act.data_ptr(), N, top,
-                            C, ff, E, _dt(h), _st()), "moe_up")
-    _check(lib().hyb_moe_down(act.data_ptr(), idx.data_ptr(), down.data_ptr(), ypair.data_ptr(), out.data_ptr(), N, top, C,
-                              ff, E, _dt(h), _st()), "moe_down")
+                            C, ff, E, int(bool(gated)), _dt(h), _st()), "moe_up")
+    _check(lib().hyb_moe_down(act.data_ptr(), idx.data_ptr(), wt.data_ptr() if gated else None, down.data_ptr(),
+                              ypair.data_ptr(), out.data_ptr(), N, top, C, ff, E, _dt(h), _st()), "moe_down")
     return out
 
 
-def gather_scale_rows(h: torch.Tensor, rows: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
-    """``out[i] = scale[i] * h[rows[i]]`` (int32 ``rows``, fp32 ``scale``), rounded to the activation type."""
+def gather_scale_rows(h: torch.Tensor, rows: torch.Tensor, scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[i] = scale[i] * h[rows[i]]`` (int32 ``rows``, fp32 ``scale``), rounded to the activation type; without
+    ``scale`` a plain gather."""
     if not h.is_cuda:
+        if scale is None:
+            return h[rows.long()]
         return (h[rows.long()].float() * scale.float()[:, None]).to(h.dtype)
     M = rows.numel()
     out = torch.empty(M, h.size(1), device=h.device, dtype=h.dtype)
-    _check(lib().hyb_gather_scale_rows(h.data_ptr(), _rows(h)[0], rows.data_ptr(), scale.data_ptr(), out.data_ptr(), M,
+    _check(lib().hyb_gather_scale_rows(h.data_ptr(), _rows(h)[0], rows.data_ptr(), None if scale is None else scale.data_ptr(), out.data_ptr(), M,
                                        h.size(1), _dt(h), _st()), "gather_scale_rows")
     return out
 
 
-def combine_rows(y: torch.Tensor, where: torch.Tensor, n: int, top: int) -> torch.Tensor:
-    """``out[t] = sum_k y[where[t*top + k]]`` summed in fp32 in the order of ``k`` (int32 ``where``)."""
+def combine_rows(y: torch.Tensor, where: torch.Tensor, n: int, top: int, wt: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[t] = sum_k wt[t, k] * y[where[t*top + k]]`` summed in fp32 in the order of ``k`` (int32 ``where``, fp32
+    ``wt [n, top]``; without it a plain sum)."""
     if not y.is_cuda:
-        return y[where.long()].float().view(n, top, -1).sum(1).to(y.dtype)
-    assert y.is_contiguous()
+        g = y[where.long()].float().view(n, top, -1)
+        if wt is not None:
+            g = g * wt.float().view(n, top, 1)
+        return g.sum(1).to(y.dtype)
+    assert y.is_contiguous() and (wt is None or (wt.is_contiguous() and wt.dtype == torch.float32))
     out = torch.empty(n, y.size(1), device=y.device, dtype=y.dtype)
-    _check(lib().hyb_combine_rows(y.data_ptr(), where.data_ptr(), out.data_ptr(), n, top, y.size(1), _dt(y), _st()),
-           "combine_rows")
+    _check(lib().hyb_combine_rows(y.data_ptr(), where.data_ptr(), None if wt is None else wt.data_ptr(), out.data_ptr(), n,
+                                  top, y.size(1), _dt(y), _st()), "combine_rows")
     return out
+
+
+_ACTS = {"silu": 0, "gelu_tanh": 1}
+
+
+def act_mul(gu: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    """``act(gu[:, :F]) * gu[:, F:]`` for rows ``gu [M, 2F]`` (a gated feed-forward whose gate and up projections are
+    one matrix product), evaluated in fp32, result in the activation type."""
+    M, F2 = gu.shape
+    Fh = F2 // 2
+    if not gu.is_cuda:
+        g, u = gu[:, :Fh].float(), gu[:, Fh:].float()
+        return ((F.silu(g) if act == "silu" else F.gelu(g, approximate="tanh")) * u).to(gu.dtype)
+    out = torch.empty(M, Fh, device=gu.device, dtype=gu.dtype)
+    _check(lib().hyb_act_mul_rows(gu.data_ptr(), _rows(gu)[0], out.data_ptr(), M, Fh, _ACTS[act], _dt(gu), _st()), "act_mul")
+    return out
+
+
+def scaled_branches(resid: torch.Tensor, a: torch.Tensor, ls1: Optional[torch.Tensor], b: Optional[torch.Tensor] = None,
+                    b2: Optional[torch.Tensor] = None, ls2: Optional[torch.Tensor] = None) -> None:
+    """``resid += ls1 * a + ls2 * (b + b2)`` in one pass over the fp32 residual: the update of a block whose mixer
+    (``a``) and feed-forward (``b``, plus ``b2`` when it has an always-on part) read the same normed input, each
+    branch with a learned scale per channel (absent: 1).  All sums are fp32."""
+    if resid.dtype != torch.float32:
+        raise HybridOpsError("the residual stream is fp32")
+    if not a.is_cuda:
+        y = a.float() * (ls1.float() if ls1 is not None else 1.0)
+        if b is not None:
+            f = b.float() + (b2.float() if b2 is not None else 0.0)
+            y = y + f * (ls2.float() if ls2 is not None else 1.0)
+        resid.add_(y)
+        return
+    N, C = a.shape
+    for t in (ls1, ls2):
+        if t is not None and (t.dtype != a.dtype or not t.is_contiguous()):
+            raise HybridOpsError("branch scales have the activation type")
+    _check(lib().hyb_scaled_branches(resid.data_ptr(), resid.stride(0), a.data_ptr(), _rows(a)[0],
+                                     None if ls1 is None else ls1.data_ptr(), None if b is None else b.data_ptr(),
+                                     0 if b is None else _rows(b)[0], None if b2 is None else b2.data_ptr(),
+                                     0 if b2 is None else _rows(b2)[0], None if ls2 is None else ls2.data_ptr(), N, C,
+                                     _dt(a), _st()), "scaled_branches")
 
 
 def matmul_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
