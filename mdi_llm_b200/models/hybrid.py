@@ -63,7 +63,7 @@ def write_safetensors(tensors: Dict[str, torch.Tensor], path: Union[str, Path]) 
     blobs, off = [], 0
     for name, t in tensors.items():
         t = t.detach().cpu().contiguous()
-        b = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        b = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""  # reshape: a scalar has no axis to view
         header[name] = {"dtype": names[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(b)]}
         blobs.append(b)
         off += len(b)
