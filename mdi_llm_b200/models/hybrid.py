@@ -407,8 +407,8 @@ class WindowAttention(nn.Module, _Fused):
         per = max(1, self.score_bytes // (Hh * W * W * 4))
         for r0, n, slot, p0 in plan.seqs:
             head = min(n, (-p0) % W)  # tokens that complete a block begun in an earlier step
-            if head:
-                self._band(out, q, cache, slot, r0, p0, 0, head, (p0 // W) * W, 0)
+            for a in range(0, head, self.query_block):
+                self._band(out, q, cache, slot, r0, p0, a, min(head, a + self.query_block), (p0 // W) * W, 0)
             full = (n - head) // W
             for c0 in range(0, full, per):
                 nc = min(per, full - c0)
@@ -421,9 +421,9 @@ class WindowAttention(nn.Module, _Fused):
                 pr = H.causal_softmax(s.view(nc * Hh, W, W), 0, self.scale, pdt, sink=self.sink)
                 o = torch.bmm(pr.view(nc * G, rep * W, W), vv.to(pdt))  # [nc*G, rep*W, V]
                 out[:, r0 + a:r0 + a + nc * W] = o.view(nc, G, rep, W, V).permute(1, 2, 0, 3, 4).reshape(Hh, nc * W, V)
-            a = head + full * W
-            if a < n:
-                self._band(out, q, cache, slot, r0, p0, a, n, p0 + a, 0)
+            tail = head + full * W
+            for a in range(tail, n, self.query_block):
+                self._band(out, q, cache, slot, r0, p0, a, min(n, a + self.query_block), p0 + tail, 0)
         return out
 
 

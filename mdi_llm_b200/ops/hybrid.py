@@ -550,7 +550,8 @@ def window_attn(q: torch.Tensor, g: Optional[torch.Tensor], cache: torch.Tensor,
                                  0 if g is None else _rows(g)[0], cache.data_ptr(), cache.stride(0), plan.meta.data_ptr(),
                                  plan.tok_seq.data_ptr(), out.data_ptr(), N, H, G, D, V, float(scale), int(window), nsplit,
                                  None if pa is None else pa.data_ptr(), None if pm is None else pm.data_ptr(),
-                                 _MASK_KINDS[mask], int(bool(sink)), gate_mode, _dt(q), _st()), "window_attn")
+                                 _MASK_KINDS[mask if window > 0 else "window"], int(bool(sink)), gate_mode, _dt(q), _st()),
+           "window_attn")  # no mask size: every earlier position, whichever kind
     return out
 
 

@@ -231,6 +231,7 @@ def test_router_kernel_matches():
 @pytest.mark.parametrize("dev", DEVICES)
 def test_whole_prompts_and_first_tokens(dev, monkeypatch):
     monkeypatch.setattr(WindowAttention, "score_bytes", 4 * 4 * 70 * 70)  # one chunk of the widest layer per product
+    monkeypatch.setattr(WindowAttention, "query_block", 16)  # a partial chunk runs in several blocks of query rows
     d, m = build(FULL, dev)
     for n in (1, 2, 3, 4, 7, 8, 69, 70, 71, 150):  # the first tokens; the edges of the chunks of 3, 7 and 70
         t = toks(n, seed=n)
