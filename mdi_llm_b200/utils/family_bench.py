@@ -15,6 +15,12 @@ An L2 flush (a write larger than L2) separates timed iterations of the single-ke
 ``bench.py --family vudelix`` measures the pre-norm design of the family (windowed grouped-query attention, gated
 delta rule, mixture-of-experts and dense feed-forwards, per-layer token embedding) the same way, beside the sandwich
 design of the same width as the closest existing model, with its own kernels one by one.
+
+``bench.py --family labepel`` measures the parallel-block design (chunk-masked attention with a softmax sink and value
+mixing, softmax-routed gated experts plus a shared expert, layer scale, learned positions) beside the pre-norm design
+of the same width, whose windowed attention and mixture of experts are the closest existing kernels.  Decoding is
+timed inside one chunk (the prompt ends short of a chunk edge), so that a step sees about as many keys as the
+windowed design does.
 """
 from __future__ import annotations
 
@@ -24,7 +30,7 @@ from typing import Any, Callable, Dict, List
 
 import torch
 
-__all__ = ["run_family_compare", "hybrid_bench_config", "vudelix_bench_config"]
+__all__ = ["run_family_compare", "hybrid_bench_config", "vudelix_bench_config", "labepel_bench_config"]
 
 
 def vudelix_bench_config(width: int, window: int = 1024) -> Dict[str, Any]:
@@ -40,6 +46,17 @@ def vudelix_bench_config(width: int, window: int = 1024) -> Dict[str, Any]:
               {"type": "channel_delta", "mixer": dict(delta), "mlp": moe}, {"type": "attention", "mixer": dict(att), "mlp": dense}]
     return {"architecture": "Vudelix", "vocab": 32000, "width": width, "layers": layers, "norm": {"eps": 1e-6},
             "residual_mult": 0.5, "token_side": {"dim": 64}}
+
+
+def labepel_bench_config(width: int, chunk: int = 1024, positions: int = 8192) -> Dict[str, Any]:
+    """4 attention layers with experts: two of eight gated experts of width ``width`` per token plus a shared expert of
+    the same width (9 width^2 weights per token, the dense ``4 * width`` feed-forward has 8)."""
+    h = width // 128
+    att = {"heads": h, "kv_heads": max(1, h // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": chunk},
+           "v_mix": True}
+    moe = {"kind": "moe", "expert": {"ff": width}, "router": {"experts": 8, "top": 2}, "shared": {"ff": width}}
+    return {"architecture": "Labepel", "vocab": 32000, "width": width, "max_positions": positions, "norm": {"eps": 1e-6},
+            "layers": [{"type": "attention", "mixer": dict(att), "mlp": dict(moe)} for _ in range(4)]}
 
 
 def hybrid_bench_config(width: int) -> Dict[str, Any]:
@@ -89,7 +106,8 @@ def _hybrid(width: int, prompt_len: int, batch: int, steps: int, warmup: int, de
     from ..parallel.hybrid_runner import HybridRunner
 
     dev = torch.device("cuda")
-    cfg = HybridConfig.from_dict(hybrid_bench_config(width) if design == "hybrid" else vudelix_bench_config(width))
+    make = {"hybrid": hybrid_bench_config, "vudelix": vudelix_bench_config, "labepel": labepel_bench_config}[design]
+    cfg = HybridConfig.from_dict(make(width))
     model = HybridLM(cfg, {}).init_random(dev, torch.bfloat16, seed=1)
     params = sum(p.numel() for p in model.tensor_map().values())
     out: Dict[str, Any] = {"params_m": round(params / 1e6, 1), "layer_params_m": round((params - model.embed.numel()) / 1e6, 1)}
@@ -109,15 +127,19 @@ def _hybrid(width: int, prompt_len: int, batch: int, steps: int, warmup: int, de
     out["prefill_tok_s"] = round(prompt_len / ms * 1e3, 1)
     out["prefill_ms"] = round(ms, 3)
     del runners
+    # the chunk-masked design decodes up to the end of the prompt's last chunk, not across its edge
+    context = prompt if design != "labepel" else prompt[: max(1, prompt_len - steps - warmup - 8)]
+    out["decode_context"] = len(context)
     for b in (1, batch):
         r = HybridRunner(model, S, n_slots=b)
-        r.step([(i, prompt) for i in range(b)])
+        r.step([(i, context) for i in range(b)])
         tok = [(i, [1]) for i in range(b)]
         ms = _time(lambda: r.step(tok), steps, warmup)
         out[f"decode_tok_s_b{b}"] = round(b / ms * 1e3, 1)
         out[f"decode_ms_b{b}"] = round(ms, 4)
         del r
-    out["kernels"] = (_hybrid_kernels if design == "hybrid" else _vudelix_kernels)(model, prompt_len, batch)
+    kernels = {"hybrid": _hybrid_kernels, "vudelix": _vudelix_kernels, "labepel": _labepel_kernels}[design]
+    out["kernels"] = kernels(model, prompt_len, batch)
     return out
 
 
@@ -185,6 +207,85 @@ def _vudelix_kernels(model: Any, T: int, batch: int) -> List[Dict[str, Any]]:
         y = torch.randn(N, C, device=dev).to(dt)
         ms = _time(lambda: H.norm_accumulate(x, y, None, None, 1e-6, "none", 0.5), 5, 3, flush)
         rec("scaled_residual_add", phase, ms, N * C * 10.0, 0.0)
+        del pool
+    return rows
+
+
+def _labepel_kernels(model: Any, T: int, batch: int) -> List[Dict[str, Any]]:
+    """The parallel-block design's own kernels alone, on the prompt shape and on the decode shape; ``like`` names the
+    row of ``_vudelix_kernels`` that does the corresponding work in the pre-norm design."""
+    from ..ops import hybrid as H
+
+    pk = _peaks()
+    dev, dt = model.device, model.dtype
+    C = model.config.width
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rows: List[Dict[str, Any]] = []
+
+    def rec(name: str, like: str, phase: str, ms: float, nbytes: float, flops: float) -> None:
+        rows.append({"kernel": name, "like": like, "phase": phase, "ms": round(ms, 4), "gb_s": round(nbytes / ms / 1e6, 1),
+                     "tflops": round(flops / ms / 1e9, 2),
+                     "frac_of_roofline": round(max(nbytes / ms / 1e6 / pk["hbm_gbs"], flops / ms / 1e9 / pk["bf16_tflops"]), 4),
+                     "peaks": pk["source"]})
+
+    blk = model.blocks[1]  # a layer that blends its values with the first layer's
+    att, moe = blk.mix, blk.mlp
+    Hh, G, D, V, W = att.H, att.G, att.D, att.V, att.window
+    first = lambda pos: (pos // W) * W if W else 0  # noqa: E731 - first visible key of a position
+    for phase, lengths, starts in (("prefill", [T], [0]), ("decode", [1] * batch, [max(0, T - 8)] * batch)):
+        n_seq, N = len(lengths), sum(lengths)
+        pool = model.new_pool(n_seq, T + 8)
+        plan = H.BatchPlan.make(lengths, list(range(n_seq)), starts, dev)
+        cache = pool.runs[1]["cache"]
+        cache.normal_()
+        tok = torch.randint(0, model.config.vocab, (N,), device=dev, dtype=torch.int32)
+        ms = _time(lambda: H.embed_rows(model.embed, tok, model.pos, plan), 5, 3, flush)
+        rec("embed_rows[positions]", "", phase, ms, N * C * 8.0, 0.0)
+        h = torch.randn(N, C, device=dev).to(dt)
+        p = H.linear(h, att.w_in, att.b_in)
+        q, g, v = att.col(p, "q"), att.col(p, "g"), att.col(p, "v")
+        vf = torch.randn_like(v)
+        pairs = sum(s + i + 1 - first(s + i) for n, s in zip(lengths, starts) for i in range(n))
+        ms = _time(lambda: H.window_append(q, att.col(p, "k"), v, None, cache, plan, Hh, G, D, V, 0, 1e-6, att.q_norm,
+                                           att.k_norm, vf, att.lam), 5, 3, flush)
+        rec("window_append[weights, value mixing]", "window_append", phase, ms,
+            2.0 * N * (2 * Hh * D + 2 * G * (D + V) + G * V), 0.0)
+        if phase == "prefill":
+            ms = _time(lambda: H.headmajor_gate(att._chunked(q, cache, plan), g), 5, 3, flush)
+            rec("chunk_attn(gemm+softmax)", "window_attn_banded(gemm+softmax)", phase, ms,
+                2.0 * N * (Hh * (D + 2 * V) + G * (D + V)), 2.0 * Hh * pairs * (D + V))
+            nb = min(N, W) if W else min(N, att.query_block)
+            s32 = torch.randn(max(1, N // nb) * Hh, nb, nb, device=dev)
+            ms = _time(lambda: H.causal_softmax(s32, 0, att.scale, torch.float32, sink=att.sink), 5, 3, flush)
+            rec("causal_softmax[sink, fp32 weights]", "causal_softmax[window]", phase, ms, s32.numel() * 8.0, 0.0)
+            del s32
+        else:
+            ms = _time(lambda: H.window_attn(q, g, cache, plan, Hh, G, D, V, att.scale, W, mask=att.mask_kind, sink=att.sink),
+                       5, 3, flush)
+            keys = sum(s + 1 - first(s) for s in starts)
+            rec("window_attn[chunk, sink, channel gate]", "window_attn", phase, ms,
+                2.0 * G * keys * (D + V) + 2.0 * N * Hh * (D + 2 * V), 2.0 * Hh * pairs * (D + V))
+        z = H.linear_f32(h, moe.router32, moe.router_b32)
+        ms = _time(lambda: H.router_topk(z, moe.top, "softmax"), 5, 3, flush)
+        rec("router_topk[softmax]", "router_topk", phase, ms, 4.0 * N * (moe.E + 2 * moe.top), 0.0)
+        ms = _time(lambda: moe(h), 5, 3, flush)
+        wbytes = 2.0 * 3 * C * moe.ff * min(moe.E, N * moe.top)
+        form = "index-driven" if N * moe.top <= moe.gemv_max else "grouped gemm"
+        rec(f"moe_experts[{form}, gated]", f"moe_experts[{form}]", phase, ms, wbytes + 2.0 * N * C * (1 + moe.top),
+            6.0 * N * moe.top * C * moe.ff)
+        sh = moe.shared
+        ms = _time(lambda: sh(h), 5, 3, flush)
+        rec("shared_expert(gemm+silu*up)", "dense_ff(gemm+gelu)", phase, ms, 2.0 * 3 * C * sh.down.size(1) + 4.0 * N * C,
+            6.0 * N * C * sh.down.size(1))
+        gu = H.linear(h, sh.w_in)
+        ms = _time(lambda: H.act_mul(gu), 5, 3, flush)
+        rec("act_mul", "", phase, ms, 2.0 * N * 3 * sh.down.size(1), 0.0)
+        x = torch.randn(N, C, device=dev)
+        ms = _time(lambda: H.norm_rows(x, blk.norm1.w, None, 1e-6, "rms", dt, 1.0), 5, 3, flush)
+        rec("rms_norm[1 + w]", "rms_norm", phase, ms, N * C * 6.0, 0.0)
+        ya, yb, yc = (torch.randn(N, C, device=dev).to(dt) for _ in range(3))
+        ms = _time(lambda: H.scaled_branches(x, ya, blk.ls1, yb, yc, blk.ls2), 5, 3, flush)
+        rec("scaled_branches", "scaled_residual_add", phase, ms, N * C * 14.0, 0.0)
         del pool
     return rows
 
@@ -328,6 +429,20 @@ def run_family_compare(widths: List[int], prompt_len: int = 2048, batch: int = 8
             torch.cuda.empty_cache()
             results.append({"width": w, "vudelix": new, "hybrid": old})
         return {"metric": "family_compare", "family": "vudelix", "dtype": "bf16", "data": "synthetic", "prompt_len": prompt_len,
+                "decode_batch": batch, "steps": steps, "warmup": warmup, "l2": "flushed between single-kernel timings",
+                "results": results}
+    if family == "labepel":
+        for w in widths:
+            new = _hybrid(w, prompt_len, batch, steps, warmup, "labepel")
+            torch.cuda.empty_cache()
+            old = _hybrid(w, prompt_len, batch, steps, warmup, "vudelix")
+            torch.cuda.empty_cache()
+            theirs = {(k["kernel"], k["phase"]): k["frac_of_roofline"] for k in old["kernels"]}
+            for k in new["kernels"]:  # how far from its roofline, relative to the like kernel of the other design
+                other = theirs.get((k["like"], k["phase"]))
+                k["roofline_vs_like"] = round(k["frac_of_roofline"] / other, 3) if other else None
+            results.append({"width": w, "labepel": new, "vudelix": old})
+        return {"metric": "family_compare", "family": "labepel", "dtype": "bf16", "data": "synthetic", "prompt_len": prompt_len,
                 "decode_batch": batch, "steps": steps, "warmup": warmup, "l2": "flushed between single-kernel timings",
                 "results": results}
     for w in widths:
