@@ -35,6 +35,20 @@ __device__ __forceinline__ void load8(const bf16* p, float* f) {
   }
 }
 
+__device__ __forceinline__ void store8(float* p, const float* f) {
+  *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+}
+__device__ __forceinline__ void store8(bf16* p, const float* f) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -1053,7 +1067,7 @@ __global__ void window_attn_kernel(const T* __restrict__ q, long long q_stride, 
                                    const int* __restrict__ meta, const int* __restrict__ tok_seq, T* __restrict__ out,
                                    int H, int G, int D, int V, float scale, int window, int nsplit,
                                    float* __restrict__ part_acc, float* __restrict__ part_ml, int mask_kind, int sink,
-                                   int gate_mode) {
+                                   int gate_mode, int vec) {
   extern __shared__ float sm[];
   int rep = H / G;
   float* qs = sm;                       // [rep][D]
@@ -1075,13 +1089,50 @@ __global__ void window_attn_kernel(const T* __restrict__ q, long long q_stride, 
   __syncthreads();
   for (int j0 = lo + (int)blockIdx.z * WT_TILE; j0 <= pos; j0 += WT_TILE * nsplit) {
     __syncthreads();
-    for (int i = threadIdx.x; i < WT_TILE * D; i += blockDim.x) {
-      int j = i / D, d = i - j * D;
-      Kt[j * (D + 1) + d] = j0 + j <= pos ? to_f(base[(size_t)(j0 + j) * rowlen + g * D + d]) : 0.f;
-    }
-    for (int i = threadIdx.x; i < WT_TILE * V; i += blockDim.x) {
-      int j = i / V, d = i - j * V;
-      Vt[i] = j0 + j <= pos ? to_f(base[(size_t)(j0 + j) * rowlen + G * D + g * V + d]) : 0.f;
+    if (vec) {
+      // 8 values per load, four loads of a thread in flight before the first is used: the tile costs one or two
+      // trips to memory instead of one per value
+      int dv = D >> 3, vv = V >> 3;
+      int nk = WT_TILE * dv, nt = nk + WT_TILE * vv;
+      for (int i0 = threadIdx.x; i0 < nt; i0 += 4 * blockDim.x) {
+        float f[4][8];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          int i = i0 + u * blockDim.x;
+          if (i < nt) {
+            bool isk = i < nk;
+            int ii = isk ? i : i - nk, per = isk ? dv : vv;
+            int j = ii / per, c = ii - j * per;
+            if (j0 + j <= pos) {
+              load8(base + (size_t)(j0 + j) * rowlen + (isk ? g * D : G * D + g * V) + c * 8, f[u]);
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[u][e] = 0.f;
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          int i = i0 + u * blockDim.x;
+          if (i < nt) {
+            bool isk = i < nk;
+            int ii = isk ? i : i - nk, per = isk ? dv : vv;
+            int j = ii / per, c = ii - j * per;
+            float* dst = isk ? Kt + j * (D + 1) + c * 8 : Vt + j * V + c * 8;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) dst[e] = f[u][e];
+          }
+        }
+      }
+    } else {
+      for (int i = threadIdx.x; i < WT_TILE * D; i += blockDim.x) {
+        int j = i / D, d = i - j * D;
+        Kt[j * (D + 1) + d] = j0 + j <= pos ? to_f(base[(size_t)(j0 + j) * rowlen + g * D + d]) : 0.f;
+      }
+      for (int i = threadIdx.x; i < WT_TILE * V; i += blockDim.x) {
+        int j = i / V, d = i - j * V;
+        Vt[i] = j0 + j <= pos ? to_f(base[(size_t)(j0 + j) * rowlen + G * D + g * V + d]) : 0.f;
+      }
     }
     __syncthreads();
     float s = -INFINITY;
@@ -1138,29 +1189,39 @@ __global__ void window_attn_kernel(const T* __restrict__ q, long long q_stride, 
   }
 }
 
-// Merge of the key shares of window_attn_kernel: one block per (token, head).
+// Merge of the key shares of window_attn_kernel: one warp per (token, head), nsplit <= 32.  Lane s reads share s's
+// running maximum and denominator (one round of loads instead of a chain of nsplit), the weights exp(m_s - M) are
+// handed round by shuffles while lane d sums channel d over the shares.
 template <typename T>
 __global__ void window_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                       const T* __restrict__ gate, long long g_stride, T* __restrict__ out, int N, int H,
                                       int V, int nsplit, int sink, int gate_mode) {
-  int t = blockIdx.x, h = blockIdx.y;
-  float M = sink ? 0.f : -INFINITY;
-  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, part_ml[2 * (((size_t)s * N + t) * H + h)]);
-  float l = sink ? expf(-M) : 0.f;
-  for (int s = 0; s < nsplit; ++s) {
-    size_t row = ((size_t)s * N + t) * H + h;
-    l += part_ml[2 * row + 1] * expf(part_ml[2 * row] - M);
+  int t = blockIdx.x, h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (h >= H) return;
+  float ms = -INFINITY, ls = 0.f;
+  if (lane < nsplit) {
+    const float* ml = part_ml + 2 * (((size_t)lane * N + t) * H + h);
+    ms = ml[0];
+    ls = ml[1];
   }
+  float M = warp_max(ms);
+  if (sink) M = fmaxf(M, 0.f);
+  float ws = lane < nsplit ? expf(ms - M) : 0.f;  // a share without keys: exp(-inf) = 0
+  float l = warp_sum(ls * ws) + (sink ? expf(-M) : 0.f);
   float gt = gate && gate_mode == 1 ? sigmoidf_(to_f(gate[(size_t)t * g_stride + h])) : 1.f;
-  for (int d = threadIdx.x; d < V; d += blockDim.x) {
+  for (int d0 = 0; d0 < V; d0 += 32) {
+    int d = d0 + lane;
     float a = 0.f;
+#pragma unroll 4
     for (int s = 0; s < nsplit; ++s) {
-      size_t row = ((size_t)s * N + t) * H + h;
-      a += part_acc[row * V + d] * expf(part_ml[2 * row] - M);
+      float w = __shfl_sync(0xffffffffu, ws, s);
+      if (d < V) a += part_acc[((((size_t)s * N + t) * H + h)) * V + d] * w;
     }
-    float o = a * gt / l;
-    if (gate && gate_mode == 2) o *= sigmoidf_(to_f(gate[(size_t)t * g_stride + (size_t)h * V + d]));
-    out[(size_t)t * H * V + (size_t)h * V + d] = from_f<T>(o);
+    if (d < V) {
+      float o = a * gt / l;
+      if (gate && gate_mode == 2) o *= sigmoidf_(to_f(gate[(size_t)t * g_stride + (size_t)h * V + d]));
+      out[(size_t)t * H * V + (size_t)h * V + d] = from_f<T>(o);
+    }
   }
 }
 
@@ -1392,6 +1453,24 @@ __global__ void act_mul_rows_kernel(const T* __restrict__ in, long long in_strid
   out[i] = from_f<T>((act == 0 ? siluf_(g) : gelu_tanhf_(g)) * u);
 }
 
+// The same, 8 values per thread with 16-byte loads and stores (F and the row stride multiples of 8, bases aligned).
+template <typename T>
+__global__ void act_mul_rows_vec_kernel(const T* __restrict__ in, long long in_stride, T* __restrict__ out, int F, int act,
+                                        long long total8) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total8) return;
+  int f8 = F >> 3;
+  long long r = i / f8;
+  int c = (int)(i - r * f8) * 8;
+  const T* row = in + (size_t)r * in_stride;
+  float g[8], u[8];
+  load8(row + c, g);
+  load8(row + F + c, u);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) g[e] = (act == 0 ? siluf_(g[e]) : gelu_tanhf_(g[e])) * u[e];
+  store8(out + (size_t)r * F + c, g);
+}
+
 // x[r, c] += ls1[c] * a[r, c] + ls2[c] * (b[r, c] + b2[r, c]): the residual update of a block whose mixer and
 // feed-forward read the same normed input, each branch with a learned scale per channel.  b, b2 and the scales are
 // optional (absent scale = 1); x is the fp32 residual.
@@ -1447,24 +1526,27 @@ int hyb_window_attn(const void* q, long long q_stride, const void* gate, long lo
   if (nsplit < 1 || (nsplit > 1 && (!part_acc || !part_ml))) return -2;
   size_t smem = ((size_t)rep * D + (size_t)WT_TILE * (D + 1) + (size_t)WT_TILE * V) * sizeof(float);
   if (smem > 220 * 1024) return -3;
-  dim3 grid(N, G, nsplit), cgrid(N, H);
+  if (nsplit > 32) return -3;  // the merge gives each key share a lane
+  dim3 grid(N, G, nsplit), cgrid(N, (H + 3) / 4);
+  // 16-byte loads of cache rows: every head's slice of every row starts on a 16-byte (fp32: 32-byte) boundary
+  int vec = D % 8 == 0 && V % 8 == 0 && slot_stride % 8 == 0 && (uintptr_t)cache % 32 == 0;
   cudaError_t e;
   if (dt == 0) {
     if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(window_attn_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
     window_attn_kernel<bf16><<<grid, 32 * rep, smem, st>>>((const bf16*)q, q_stride, (const bf16*)gate, g_stride,
                                                            (const bf16*)cache, slot_stride, meta, tok_seq, (bf16*)out, H,
                                                            G, D, V, scale, window, nsplit, part_acc, part_ml, mask_kind, sink,
-                                                           gate_mode);
+                                                           gate_mode, vec);
     if (nsplit > 1)
-      window_combine_kernel<bf16><<<cgrid, 64, 0, st>>>(part_acc, part_ml, (const bf16*)gate, g_stride, (bf16*)out, N, H, V, nsplit, sink, gate_mode);
+      window_combine_kernel<bf16><<<cgrid, 128, 0, st>>>(part_acc, part_ml, (const bf16*)gate, g_stride, (bf16*)out, N, H, V, nsplit, sink, gate_mode);
   } else {
     if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(window_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
     window_attn_kernel<float><<<grid, 32 * rep, smem, st>>>((const float*)q, q_stride, (const float*)gate, g_stride,
                                                             (const float*)cache, slot_stride, meta, tok_seq, (float*)out,
                                                             H, G, D, V, scale, window, nsplit, part_acc, part_ml, mask_kind, sink,
-                                                            gate_mode);
+                                                            gate_mode, vec);
     if (nsplit > 1)
-      window_combine_kernel<float><<<cgrid, 64, 0, st>>>(part_acc, part_ml, (const float*)gate, g_stride, (float*)out, N, H, V, nsplit, sink, gate_mode);
+      window_combine_kernel<float><<<cgrid, 128, 0, st>>>(part_acc, part_ml, (const float*)gate, g_stride, (float*)out, N, H, V, nsplit, sink, gate_mode);
   }
   return (int)cudaGetLastError();
 }
@@ -1570,6 +1652,13 @@ int hyb_act_mul_rows(const void* in, long long in_stride, void* out, long long r
   long long total = rows * F;
   if (total == 0) return 0;
   if (act < 0 || act > 1) return -3;
+  if (F % 8 == 0 && in_stride % 8 == 0 && (uintptr_t)in % 32 == 0 && (uintptr_t)out % 32 == 0) {
+    long long total8 = total / 8;
+    unsigned vb = (unsigned)((total8 + 255) / 256);
+    HYB_DISPATCH(dt, (act_mul_rows_vec_kernel<bf16><<<vb, 256, 0, st>>>((const bf16*)in, in_stride, (bf16*)out, F, act, total8)),
+                 (act_mul_rows_vec_kernel<float><<<vb, 256, 0, st>>>((const float*)in, in_stride, (float*)out, F, act, total8)));
+    return (int)cudaGetLastError();
+  }
   unsigned blocks = (unsigned)((total + 255) / 256);
   HYB_DISPATCH(dt, (act_mul_rows_kernel<bf16><<<blocks, 256, 0, st>>>((const bf16*)in, in_stride, (bf16*)out, F, act, total)),
                (act_mul_rows_kernel<float><<<blocks, 256, 0, st>>>((const float*)in, in_stride, (float*)out, F, act, total)));

@@ -541,7 +541,7 @@ def window_attn(q: torch.Tensor, g: Optional[torch.Tensor], cache: torch.Tensor,
     out = torch.empty(N, H * V, device=q.device, dtype=q.dtype)
     blocks = N * G
     tiles = (window + 31) // 32 if window > 0 else 16
-    nsplit = split or (1 if blocks >= 2 * _SM_TARGET else max(1, min(32, tiles, (2 * _SM_TARGET + blocks - 1) // blocks)))
+    nsplit = min(32, split) or (1 if blocks >= 4 * _SM_TARGET else max(1, min(32, tiles, (4 * _SM_TARGET + blocks - 1) // blocks)))
     pa = pm = None
     if nsplit > 1:
         pa = torch.empty(nsplit, N, H, V, device=q.device, dtype=torch.float32)

@@ -132,8 +132,9 @@ def _hybrid(width: int, prompt_len: int, batch: int, steps: int, warmup: int, de
     out["decode_context"] = len(context)
     for b in (1, batch):
         r = HybridRunner(model, S, n_slots=b)
-        r.step([(i, context) for i in range(b)])
-        tok = [(i, [1]) for i in range(b)]
+        # every stream its own prompt and tokens: identical streams would all choose the same experts
+        r.step([(i, torch.randint(0, cfg.vocab, (len(context),)).tolist()) for i in range(b)])
+        tok = [(i, [1 + 37 * i]) for i in range(b)]
         ms = _time(lambda: r.step(tok), steps, warmup)
         out[f"decode_tok_s_b{b}"] = round(b / ms * 1e3, 1)
         out[f"decode_ms_b{b}"] = round(ms, 4)
