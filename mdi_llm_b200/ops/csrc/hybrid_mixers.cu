@@ -1402,6 +1402,142 @@ __global__ void moe_pairs_kernel(const void* __restrict__ xin, long long x_strid
   }
 }
 
+// The same work for bf16 weights with K a multiple of 8, streamed: the block's slab of weight rows (32 rows; with a
+// gate, the 32 gate rows and the 32 up rows) crosses shared memory in chunks of KC columns through a ring of
+// MS_STAGES 16 KB stages filled by 16-byte asynchronous copies, three chunks in flight while one is used, so the
+// bytes in flight per SM do not depend on how many warps wait.  A warp owns rows w, w+8, w+16, w+24 of the slab and
+// keeps their sums for up to MOE_PCH pairs; a lane takes 8 columns of a chunk (with a gate: lanes 0-15 the gate row,
+// lanes 16-31 the up row of the same output).
+#define MS_STAGES 4
+#define MS_STAGE_ELEMS 8192
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+template <int MODE>
+__global__ void __launch_bounds__(256) moe_pairs_stream_kernel(const void* __restrict__ xin, long long x_stride,
+                                                               const int* __restrict__ idx, const float* __restrict__ wt,
+                                                               const bf16* __restrict__ w, float* __restrict__ y, int P,
+                                                               int top, int K, int R, int pch) {
+  constexpr int KC = MODE == 2 ? 128 : 256;  // columns per chunk
+  constexpr int LPR = KC / 8;                // lanes per row of a chunk
+  extern __shared__ __align__(16) unsigned char ms_raw[];
+  float* xs = reinterpret_cast<float*>(ms_raw);                          // [pch][K]
+  bf16* ring = reinterpret_cast<bf16*>(ms_raw + (size_t)pch * K * 4);    // [MS_STAGES][rows][KC]
+  __shared__ int match[MOE_PCH];
+  __shared__ int s_cnt, s_next;
+  int e = blockIdx.x, f0 = blockIdx.y * MOE_ROWS;
+  int lane = threadIdx.x & 31, wp = threadIdx.x >> 5;
+  const bf16* we = w + (size_t)e * (MODE == 2 ? 2 : 1) * R * K;
+  int nchunks = (K + KC - 1) / KC;
+  if (threadIdx.x == 0) s_next = 0;
+  __syncthreads();
+  while (true) {
+    if (threadIdx.x == 0) {
+      int c = 0, p = s_next;
+      for (; p < P && c < pch; ++p)
+        if (idx[p] == e) match[c++] = p;
+      s_cnt = c;
+      s_next = p;
+    }
+    __syncthreads();
+    int cnt = s_cnt;
+    if (cnt == 0) return;
+    // fill one stage: 1024 vectors of 8 weights, four per thread; rows past R and columns past K become zeros
+    auto issue = [&](int kc, int stage) {
+      bf16* st = ring + (size_t)stage * MS_STAGE_ELEMS;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        int v = threadIdx.x + 256 * u;
+        int sr = v / LPR, cv = v - sr * LPR;
+        int f = f0 + (sr & (MOE_ROWS - 1)), k = kc * KC + cv * 8;
+        bf16* dst = st + sr * KC + cv * 8;
+        if (f < R && k < K) {
+          size_t row = MODE == 2 && sr >= MOE_ROWS ? (size_t)R + f : (size_t)f;
+          cp_async16(dst, we + row * K + k);
+        } else {
+          *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+    };
+#pragma unroll
+    for (int s = 0; s < MS_STAGES - 1; ++s) {
+      if (s < nchunks) issue(s, s);
+      cp_async_commit();
+    }
+    for (int m = 0; m < cnt; ++m) {  // the pairs' inputs, while the first chunks travel
+      int p = match[m];
+      if (MODE == 0) {
+        const bf16* x = (const bf16*)xin + (size_t)(p / top) * x_stride;
+        float sc = wt[p];
+        for (int c = threadIdx.x; c < K; c += blockDim.x) xs[m * K + c] = to_f(from_f<bf16>(sc * to_f(x[c])));
+      } else if (MODE == 2) {
+        const bf16* x = (const bf16*)xin + (size_t)(p / top) * x_stride;
+        for (int c = threadIdx.x; c < K; c += blockDim.x) xs[m * K + c] = to_f(x[c]);
+      } else {
+        const float* x = (const float*)xin + (size_t)p * x_stride;
+        for (int c = threadIdx.x; c < K; c += blockDim.x) xs[m * K + c] = x[c];
+      }
+    }
+    float acc[4][MOE_PCH];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int m = 0; m < MOE_PCH; ++m) acc[i][m] = 0.f;
+    int half = MODE == 2 ? lane >> 4 : 0, hl = MODE == 2 ? lane & 15 : lane;
+    for (int kc = 0; kc < nchunks; ++kc) {
+      cp_async_wait<MS_STAGES - 2>();  // this thread's copies of chunk kc have landed
+      __syncthreads();                 // everybody's have, and everybody is done with chunk kc - 1
+      int nk = kc + MS_STAGES - 1;
+      if (nk < nchunks) issue(nk, nk % MS_STAGES);  // into the stage chunk kc - 1 occupied
+      cp_async_commit();
+      const bf16* st = ring + (size_t)(kc % MS_STAGES) * MS_STAGE_ELEMS;
+      int k = kc * KC + hl * 8;
+      if (k < K) {
+        float wv[4][8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) load8(st + (half * MOE_ROWS + wp + 8 * i) * KC + hl * 8, wv[i]);
+#pragma unroll
+        for (int m = 0; m < MOE_PCH; ++m)
+          if (m < cnt) {
+            const float4* xv = reinterpret_cast<const float4*>(xs + (size_t)m * K + k);
+            float4 x0 = xv[0], x1 = xv[1];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              acc[i][m] += wv[i][0] * x0.x + wv[i][1] * x0.y + wv[i][2] * x0.z + wv[i][3] * x0.w + wv[i][4] * x1.x +
+                           wv[i][5] * x1.y + wv[i][6] * x1.z + wv[i][7] * x1.w;
+          }
+      }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int f = f0 + wp + 8 * i;
+#pragma unroll
+      for (int m = 0; m < MOE_PCH; ++m) {
+        if (m < cnt) {  // cnt is the same for the whole block: the shuffles below are not divergent
+          float v = acc[i][m];
+          if (MODE == 2) {
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            float g = __shfl_sync(0xffffffffu, v, 0), u = __shfl_sync(0xffffffffu, v, 16);
+            v = siluf_(g) * u;
+          } else {
+            v = warp_sum(v);
+            if (MODE == 0) { v = fmaxf(v, 0.f); v = v * v; }
+          }
+          if (lane == 0 && f < R) y[(size_t)match[m] * R + f] = v;
+        }
+      }
+    }
+    __syncthreads();
+  }
+}
+
 // out[t, c] = sum_k wt[t * top + k] * y[t * top + k, c] (wt absent: plain sum), summed in the order of k.
 template <typename T>
 __global__ void moe_sum_kernel(const float* __restrict__ y, const float* __restrict__ wt, T* __restrict__ out, int top,
@@ -1589,6 +1725,20 @@ static int launch_moe_pairs(const void* x, long long x_stride, const int* idx, c
   // shared memory only for the pairs there can be, and at most 64 KB while more than one pair is staged: three
   // blocks per SM keep more weight loads in flight than one block that serves four pairs at once
   int pch = P < MOE_PCH ? P : MOE_PCH;
+  if constexpr (sizeof(T) == 2) {
+    if (K % 8 == 0 && (uintptr_t)w % 16 == 0) {  // streamed form: 64 KB of stages beside at most 32 KB of inputs
+      int spch = pch;
+      while (spch > 1 && (size_t)spch * K * sizeof(float) > 32 * 1024) --spch;
+      size_t ssm = (size_t)spch * K * sizeof(float) + (size_t)MS_STAGES * MS_STAGE_ELEMS * sizeof(bf16);
+      if (ssm <= 200 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(moe_pairs_stream_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ssm);
+        if (e != cudaSuccess) return (int)e;
+        dim3 sgrid(E, (R + MOE_ROWS - 1) / MOE_ROWS);
+        moe_pairs_stream_kernel<MODE><<<sgrid, 256, ssm, st>>>(x, x_stride, idx, wt, (const bf16*)w, y, P, top, K, R, spch);
+        return (int)cudaGetLastError();
+      }
+    }
+  }
   while (pch > 1 && (size_t)pch * K * sizeof(float) > 64 * 1024) --pch;
   size_t smem = (size_t)pch * K * sizeof(float);
   if (smem > 200 * 1024) return -3;

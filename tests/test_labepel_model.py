@@ -436,7 +436,8 @@ def test_append_normalises_with_weights_mixes_values_and_writes_the_cache(dev):
 
 # ---- mixture of experts: the two forms against a plain loop -------------------------------------------------
 @pytest.mark.parametrize("dev", DEVICES)
-@pytest.mark.parametrize("sizes", [(40, 24, 6, 3), (33, 18, 4, 1), (7, 8, 2, 2)], ids=["top3", "top1", "all"])
+@pytest.mark.parametrize("sizes", [(40, 24, 6, 3), (33, 18, 4, 1), (7, 8, 2, 2), (1160, 1096, 3, 2)],
+                         ids=["top3", "top1", "all", "long_rows"])  # long rows: several chunks of a streamed weight row, the last partial
 def test_expert_forms_agree_with_a_plain_loop(dev, sizes, monkeypatch):
     device, dtype = dev
     C, ff, E, top = sizes
