@@ -166,6 +166,14 @@ class _Fused:
         a, b = self.cols[name]
         return p[:, a:b]
 
+    def rebase(self, rows: torch.Tensor) -> None:
+        """Move the fused weight into ``rows`` (same shape, a slice of a larger matrix that already holds its values):
+        the originals become views of that."""
+        assert rows.shape == self.w_in.shape
+        self.w_in = rows
+        for n, (a, b) in self.cols.items():
+            getattr(self, n).data = rows[a:b]
+
 
 class LatentAttention(nn.Module, _Fused):
     tensor_names = {"dq": "dq", "dq.norm": "dq_norm", "uq": "uq", "dkv": "dkv", "dkv.norm": "dkv_norm", "uk": "uk",
@@ -345,8 +353,11 @@ class WindowAttention(nn.Module, _Fused):
         if self.nrot:
             self.inv_freq = H.scaled_inv_freq(self.nrot, self.rot_base, self.rot_scaling, self.q.device)
 
-    def forward(self, h: torch.Tensor, plan: H.BatchPlan, st: Dict[str, torch.Tensor]) -> torch.Tensor:
-        p = H.linear(h, self.w_in, self.b_in)
+    def forward(self, h: torch.Tensor, plan: H.BatchPlan, st: Dict[str, torch.Tensor],
+                p: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``p``: the fused input projection of ``h`` when the caller has already computed it."""
+        if p is None:
+            p = H.linear(h, self.w_in, self.b_in)
         q, g, v = self.col(p, "q"), self.col(p, "g"), self.col(p, "v")
         v_first = lam = None
         if self.v_mix:
@@ -440,8 +451,9 @@ class GatedFF(nn.Module, _Fused):
     def finalize(self) -> None:
         self.fuse(("gate", "up"))
 
-    def forward(self, h: torch.Tensor) -> torch.Tensor:
-        return H.linear(H.act_mul(H.linear(h, self.w_in), self.act), self.down)
+    def forward(self, h: torch.Tensor, gu: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``gu``: the gate and up projections of ``h`` side by side when the caller has already computed them."""
+        return H.linear(H.act_mul(H.linear(h, self.w_in) if gu is None else gu, self.act), self.down)
 
 
 class MoEFF(nn.Module):
@@ -629,6 +641,9 @@ class ParallelBlock(nn.Module):
         self.norm1 = _LN(width) if norm == "layer" else _RMS(width)
         self.ls1 = _param(width) if layer_scale else None
         self.ls2 = _param(width) if layer_scale and ff is not None else None
+        self.w_all: Optional[torch.Tensor] = None
+        self.b_all: Optional[torch.Tensor] = None
+        self.n_mix = 0
 
     def norm_names(self) -> List[str]:
         return ["norm1"]
@@ -639,14 +654,33 @@ class ParallelBlock(nn.Module):
     def forward(self, x: torch.Tensor, plan: H.BatchPlan, st: Dict[str, torch.Tensor], dtype: torch.dtype,
                 tokens: Optional[torch.Tensor] = None, side_table: Optional[torch.Tensor] = None) -> None:
         h = H.norm_rows(x, self.norm1.w, self.norm1.b, self.eps, self.kind, dtype, self.offset)
-        a = self.mix(h, plan, st)
+        shared = getattr(self.mlp, "shared", None)
         b = b2 = None
-        if self.mlp is not None:
-            b = self.mlp(h)
-            shared = getattr(self.mlp, "shared", None)
+        if self.w_all is not None:
+            pa = H.linear(h, self.w_all, self.b_all)
+            a = self.mix(h, plan, st, pa[:, :self.n_mix])
+            b2 = shared(h, pa[:, self.n_mix:])
+        else:
+            a = self.mix(h, plan, st)
             if shared is not None:
                 b2 = shared(h)
+        if self.mlp is not None:
+            b = self.mlp(h)
         H.scaled_branches(x, a, self.ls1, b, b2, self.ls2)
+
+    def finalize(self) -> None:
+        """Both branches read the same normed rows: the mixer's fused input projection and the shared expert's gate
+        and up projections become ONE matrix product (every output column is the same dot product as before).  The
+        two fused weights turn into row ranges of one matrix; nothing is stored twice."""
+        shared = getattr(self.mlp, "shared", None)
+        if shared is None or not isinstance(self.mix, WindowAttention):
+            return
+        self.n_mix = self.mix.w_in.size(0)
+        self.w_all = torch.cat((self.mix.w_in, shared.w_in), 0).contiguous()
+        self.mix.rebase(self.w_all[:self.n_mix])
+        shared.rebase(self.w_all[self.n_mix:])
+        if self.mix.b_in is not None:
+            self.b_all = torch.cat((self.mix.b_in, torch.zeros_like(shared.w_in[:, 0]))).contiguous()
 
 
 def _rank_of(tensors: Optional[Dict[str, torch.Tensor]], key: str, default: int) -> int:
@@ -747,6 +781,8 @@ class HybridLM(nn.Module):
             raise KeyError(f"checkpoint does not match the configuration: missing {missing[:5]}, unexpected {extra[:5]}")
         for name, p in tm.items():
             t = tensors[name]
+            if p.dim() == 0 and t.numel() == 1:  # a scalar may be stored with shape [] or [1]
+                t = t.reshape(())
             if tuple(t.shape) != tuple(p.shape):
                 raise ValueError(f"{name}: checkpoint shape {tuple(t.shape)} != expected {tuple(p.shape)}")
             p.data = t.to(device=device, dtype=dtype).contiguous()
@@ -780,6 +816,8 @@ class HybridLM(nn.Module):
             blk.mix.finalize()
             if isinstance(blk.mlp, (MoEFF, GatedFF)):
                 blk.mlp.finalize()
+            if isinstance(blk, ParallelBlock):
+                blk.finalize()
         self.dtype, self.device = self.embed.dtype, self.embed.device
         return self
 

@@ -1209,6 +1209,30 @@ __global__ void window_combine_kernel(const float* __restrict__ part_acc, const 
   float ws = lane < nsplit ? expf(ms - M) : 0.f;  // a share without keys: exp(-inf) = 0
   float l = warp_sum(ls * ws) + (sink ? expf(-M) : 0.f);
   float gt = gate && gate_mode == 1 ? sigmoidf_(to_f(gate[(size_t)t * g_stride + h])) : 1.f;
+  if ((V & 3) == 0) {  // four channels per lane, eight shares' loads in flight: the merge is a chain of round trips
+    for (int d0 = 0; d0 < V; d0 += 128) {
+      int d = d0 + 4 * lane;
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+      for (int s = 0; s < nsplit; ++s) {
+        float w = __shfl_sync(0xffffffffu, ws, s);
+        if (d < V) {
+          float4 x = *reinterpret_cast<const float4*>(part_acc + ((((size_t)s * N + t) * H + h)) * V + d);
+          a.x += x.x * w; a.y += x.y * w; a.z += x.z * w; a.w += x.w * w;
+        }
+      }
+      if (d < V) {
+        float o[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float v = o[e] * gt / l;
+          if (gate && gate_mode == 2) v *= sigmoidf_(to_f(gate[(size_t)t * g_stride + (size_t)h * V + d + e]));
+          out[(size_t)t * H * V + (size_t)h * V + d + e] = from_f<T>(v);
+        }
+      }
+    }
+    return;
+  }
   for (int d0 = 0; d0 < V; d0 += 32) {
     int d = d0 + lane;
     float a = 0.f;

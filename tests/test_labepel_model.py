@@ -387,9 +387,10 @@ def test_keys_just_inside_and_outside_the_chunk_and_far_back(dev, W):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_key_shares_of_the_decode_form_agree(dtype):
-    G, rep, D, V, W = 2, 3, 8, 6, 70
-    k, v, cache = _sharp_case(("cuda", dtype))
+@pytest.mark.parametrize("V", [6, 8, 136])  # one channel per lane; four per lane; a second pass of 128 channels
+def test_key_shares_of_the_decode_form_agree(dtype, V):
+    G, rep, D, W = 2, 3, 8, 70
+    k, v, cache = _sharp_case(("cuda", dtype), V=V)
     g = torch.Generator().manual_seed(1)
     q = (torch.randn(3, G * rep * D, generator=g) * 3).to(device="cuda", dtype=dtype)
     gate = torch.randn(3, G * rep * V, generator=g).to(device="cuda", dtype=dtype)
