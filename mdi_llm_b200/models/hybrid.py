@@ -462,7 +462,7 @@ class MoEFF(nn.Module):
     * ``expert="relu2"``, ``router="sigmoid"``: ``sum_e down_e relu(up_e (s_e h))^2`` with ``s = sigmoid(logit)`` — the
       score scales the expert's *input*;
     * ``expert="gated_silu"``, ``router="softmax"``: ``sum_e s_e down_e (silu(gate_e h) * (up_e h))`` with ``s`` the
-      softmax over the chosen logits only — the score weighs the expert's *output*.
+      softmax restricted to the selected logits — the score weighs the expert's *output*.
 
     ``shared`` (a :class:`GatedFF`, optional) is an expert every token uses; the block adds its output.  The expert
     weights are stacked at load (``up [E, ff, C]``, or ``[E, 2 ff, C]`` with an expert's gate rows before its up rows;

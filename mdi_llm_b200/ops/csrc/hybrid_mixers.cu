@@ -1057,7 +1057,7 @@ __global__ void window_append_kernel(T* __restrict__ q, long long q_stride, cons
 // With nsplit > 1 (few tokens: decoding) block z takes every nsplit-th tile and leaves its unnormalised sum, running
 // maximum and denominator in part_acc / part_ml; window_combine_kernel merges the shares and applies the gate.
 // mask_kind 0: the last `window` positions (0 = all earlier ones); 1: the positions of the token's own block of `window`
-// positions, blocks counted from position 0 of the sequence.  sink != 0: a slot of score zero without a value joins the
+// positions, blocks numbered from the first position of the sequence.  sink != 0: a slot of score zero without a value joins the
 // softmax denominator.  gate_mode 1: sigmoid(gate[t, h]) per head; 2: sigmoid(gate[t, h * V + d]) per output channel.
 #define WT_TILE 32
 #define WT_MAXV 8
@@ -1274,7 +1274,7 @@ __global__ void token_side_gate_kernel(const T* __restrict__ z, long long z_stri
 }
 
 // One thread per token: the `top` largest logits (ties to the lower index).  mode 0: scores = sigmoid(logit), each
-// on its own; mode 1: scores = softmax over the chosen logits only.
+// on its own; mode 1: scores = softmax restricted to the selected logits.
 __global__ void router_topk_kernel(const float* __restrict__ z, int* __restrict__ idx, float* __restrict__ wt, int N,
                                    int E, int top, int mode) {
   int t = blockIdx.x * blockDim.x + threadIdx.x;

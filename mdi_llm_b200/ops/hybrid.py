@@ -507,7 +507,7 @@ def window_attn(q: torch.Tensor, g: Optional[torch.Tensor], cache: torch.Tensor,
     fewer than ``window`` positions back; query head ``h`` reads key/value head ``h // (H/G)``.  Each head's output is
     multiplied by ``sigmoid(g[token, h])`` when ``g [N, H]`` is given, or channel by channel by ``sigmoid(g)`` for
     ``g [N, H*V]``.  ``mask="chunk"``: a token sees the earlier keys of its own block of ``window`` positions (blocks
-    counted from position 0 of the sequence) instead of the last ``window``.  ``sink``: the softmax denominator gains
+    numbered from the first position of the sequence) instead of the last ``window``.  ``sink``: the softmax denominator gains
     one slot of score zero without a value.  Returns ``[N, H*V]``.  The form for one-token steps and
     short portions: one block per token and key/value head, the cache tile shared by the group's query heads.
     ``split`` (CUDA): key shares per token, 0 = chosen from the batch shape and the window alone, so that a captured
@@ -564,7 +564,7 @@ _ROUTER_MODES = {"sigmoid": 0, "softmax": 1}
 def router_topk(z: torch.Tensor, top: int, mode: str = "sigmoid") -> Tuple[torch.Tensor, torch.Tensor]:
     """From fp32 router logits ``z [N, E]``: the ``top`` experts with the largest logits per token (ties go to the lower
     index) as int32 ``[N, top]`` and their scores as fp32 ``[N, top]``: ``sigmoid(z)`` of each, not renormalised
-    (``mode="sigmoid"``), or the softmax over the chosen logits only (``mode="softmax"``)."""
+    (``mode="sigmoid"``), or the softmax restricted to the selected logits (``mode="softmax"``)."""
     N, E = z.shape
     if not z.is_cuda:
         if mode == "softmax":

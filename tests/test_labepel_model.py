@@ -140,7 +140,7 @@ def test_positions_are_added_and_bounded(dev):
         HybridConfig.from_dict({**cfg_dict([att()]), "max_positions": 0})
 
 
-def test_norm_weight_is_stored_around_zero():
+def test_norm_weight_is_a_deviation_from_one():
     x = torch.randn(5, 16, generator=torch.Generator().manual_seed(0))
     w = torch.randn(16, generator=torch.Generator().manual_seed(1)) * 0.1
     got = H.norm_rows(x, w, None, 1e-2, "rms", torch.float32, w_offset=1.0)
