@@ -520,6 +520,26 @@ def test_checkpoint_roundtrip_registry_and_trace_cli(tmp_path):
     close(rd(3), want[[11]], ("cpu", torch.float32))
 
 
+def test_sample_command_line_serves_the_checkpoint(tmp_path, capsys):
+    """``sample --ckpt`` on a self-describing folder: registry -> loader -> runner -> greedy sampling; the printed ids
+    continue the byte-level prompt exactly as the oracle's argmax does."""
+    from mdi_llm_b200.cli import sample
+
+    d, m = build(all_experts(FULL), ("cpu", torch.float32))
+    ck = tmp_path / "ck"
+    ck.mkdir()
+    m.config.save(ck)
+    write_safetensors({k: v.to(torch.bfloat16) for k, v in m.state_tensors().items()}, ck / "model.safetensors")
+    assert sample.main(["--ckpt", str(ck), "--prompt", "chunks", "--n-samples", "2", "--n-tokens", "5", "--greedy",
+                        "--device", "cpu", "--dtype", "float32"]) == 0
+    out = capsys.readouterr().out
+    ids = [b % 50 for b in b"chunks"]
+    want = []
+    for _ in range(5):
+        want.append(int(oracle_logits(d, m, ids + want)[-1].argmax()))
+    assert out.count(" ".join(map(str, want))) == 2, out
+
+
 def test_config_validation():
     with pytest.raises(ValueError):
         HybridConfig.from_dict(cfg_dict([att(mlp={"kind": "moe", "expert": {"ff": 8}, "router": {"experts": 2, "top": 3}})]))
