@@ -225,7 +225,8 @@ MIXER_KEYS = {
 #   attention: mask "window" (the last mask.size positions) | "chunk" (the query's own block of mask.size positions);
 #              sink (a zero-score slot in the softmax denominator); qk_norm "unit" (divide by the RMS) | "weight" (RMS
 #              norm with a learned weight per entry, shared by the heads); bias on q, k, v; gate "head" | "channel";
-#              p32 (softmax weights stay fp32 into the weighted sum of the prompt form)
+#              p32 (the prompt form sums the values with softmax weights of more than the activation type's mantissa:
+#              fp32 weights, or with 16-bit activations their rounding and its remainder as two 16-bit operands)
 #   moe:       router "sigmoid" (independent scores) | "softmax" (over the chosen logits); router_bias; expert "relu2"
 #              (down relu(up x)^2, the score scales the input) | "gated_silu" (down (silu(gate x) * up x), the score
 #              weighs the output); a ``shared`` always-on expert is read from the layer's mlp entry

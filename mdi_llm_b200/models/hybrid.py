@@ -391,6 +391,11 @@ class WindowAttention(nn.Module, _Fused):
         vv = rows[:, G * D:].view(keys, G, V).transpose(0, 1)     # [G, keys, V]
         qh = q[r0 + a:r0 + b].view(nb, G, rep, D).permute(1, 2, 0, 3).reshape(G, rep * nb, D)
         s = H.matmul_f32(qh, kt).contiguous()
+        if self.p32 and q.dtype != torch.float32:  # weights as two 16-bit halves: the sum stays on the tensor cores
+            pr = H.causal_softmax(s.view(Hh, nb, keys), p0 + a, self.scale, q.dtype, window=window, key0=key0, sink=self.sink,
+                                  split=True)
+            out[:, r0 + a:r0 + b] = H.matmul_f32(pr.view(G, rep * nb, 2 * keys), torch.cat((vv, vv), 1)).view(Hh, nb, V)
+            return
         pdt = torch.float32 if self.p32 else q.dtype
         pr = H.causal_softmax(s.view(Hh, nb, keys), p0 + a, self.scale, pdt, window=window, key0=key0, sink=self.sink)
         out[:, r0 + a:r0 + b] = torch.bmm(pr.view(G, rep * nb, keys), vv.to(pdt)).view(Hh, nb, V)
@@ -415,6 +420,7 @@ class WindowAttention(nn.Module, _Fused):
         rep = Hh // G
         out = torch.empty(Hh, q.size(0), V, device=q.device, dtype=q.dtype)
         pdt = torch.float32 if self.p32 else q.dtype
+        split = self.p32 and q.dtype != torch.float32
         per = max(1, self.score_bytes // (Hh * W * W * 4))
         for r0, n, slot, p0 in plan.seqs:
             head = min(n, (-p0) % W)  # tokens that complete a block begun in an earlier step
@@ -429,8 +435,12 @@ class WindowAttention(nn.Module, _Fused):
                 vv = rows[:, G * D:].reshape(nc, W, G, V).permute(0, 2, 1, 3).reshape(nc * G, W, V)
                 qh = q[r0 + a:r0 + a + nc * W].reshape(nc, W, G, rep, D).permute(0, 2, 3, 1, 4).reshape(nc * G, rep * W, D)
                 s = H.matmul_f32(qh, kt).contiguous()
-                pr = H.causal_softmax(s.view(nc * Hh, W, W), 0, self.scale, pdt, sink=self.sink)
-                o = torch.bmm(pr.view(nc * G, rep * W, W), vv.to(pdt))  # [nc*G, rep*W, V]
+                if split:
+                    pr = H.causal_softmax(s.view(nc * Hh, W, W), 0, self.scale, q.dtype, sink=self.sink, split=True)
+                    o = H.matmul_f32(pr.view(nc * G, rep * W, 2 * W), torch.cat((vv, vv), 1))
+                else:
+                    pr = H.causal_softmax(s.view(nc * Hh, W, W), 0, self.scale, pdt, sink=self.sink)
+                    o = torch.bmm(pr.view(nc * G, rep * W, W), vv.to(pdt))  # [nc*G, rep*W, V]
                 out[:, r0 + a:r0 + a + nc * W] = o.view(nc, G, rep, W, V).permute(1, 2, 0, 3, 4).reshape(Hh, nc * W, V)
             tail = head + full * W
             for a in range(tail, n, self.query_block):

@@ -353,9 +353,11 @@ __global__ void latent_combine_kernel(const float* __restrict__ part_acc, const 
 // Causal softmax of fp32 score rows for the expanded (prompt) form of latent attention: row (h, i) sees keys
 // j <= first_pos + i; p = softmax(scale * s) over those, zeros elsewhere, written in the activation type.
 // sink != 0: one more slot of score zero joins the denominator (it has no value): p_j = e^{s_j} / (1 + sum e^{s_k}).
+// split != 0: a row of p is 2 * keys wide: the weights rounded to T, and behind them the remainders (weight minus its
+// rounding) rounded to T, so that a matrix product with the values stacked twice sums the weights to 16 mantissa bits.
 template <typename T>
 __global__ void causal_softmax_kernel(const float* __restrict__ s, T* __restrict__ p, int rows_per_head, int keys,
-                                      int first_pos, float scale, int window, int key0, int sink) {
+                                      int first_pos, float scale, int window, int key0, int sink, int split) {
   __shared__ float red[33];
   size_t row = blockIdx.x;
   int i = (int)(row % rows_per_head);
@@ -378,6 +380,16 @@ __global__ void causal_softmax_kernel(const float* __restrict__ s, T* __restrict
   sum = block_sum(sum, red);
   if (sink) sum += expf(-m * scale);
   float inv = 1.f / sum;
+  if (split) {
+    dst = p + row * 2 * keys;
+    for (int j = threadIdx.x; j < keys; j += blockDim.x) {
+      float v = j >= lo && j < vis ? expf((src[j] - m) * scale) * inv : 0.f;
+      T hi = from_f<T>(v);
+      dst[j] = hi;
+      dst[keys + j] = from_f<T>(v - to_f(hi));
+    }
+    return;
+  }
   for (int j = threadIdx.x; j < keys; j += blockDim.x)
     dst[j] = from_f<T>(j >= lo && j < vis ? expf((src[j] - m) * scale) * inv : 0.f);
 }
@@ -871,11 +883,11 @@ int hyb_latent_attn(const void* qlat, const void* q, long long q_stride, const v
 }
 
 int hyb_causal_softmax(const float* s, void* p, long long rows, int rows_per_head, int keys, int first_pos, float scale,
-                       int window, int key0, int sink, int dt, cudaStream_t st) {
+                       int window, int key0, int sink, int split, int dt, cudaStream_t st) {
   if (rows == 0) return 0;
   if (scale <= 0.f) return -3;  // the row maximum is taken before scaling
-  HYB_DISPATCH(dt, (causal_softmax_kernel<bf16><<<(unsigned)rows, 256, 0, st>>>(s, (bf16*)p, rows_per_head, keys, first_pos, scale, window, key0, sink)),
-               (causal_softmax_kernel<float><<<(unsigned)rows, 256, 0, st>>>(s, (float*)p, rows_per_head, keys, first_pos, scale, window, key0, sink)));
+  HYB_DISPATCH(dt, (causal_softmax_kernel<bf16><<<(unsigned)rows, 256, 0, st>>>(s, (bf16*)p, rows_per_head, keys, first_pos, scale, window, key0, sink, split)),
+               (causal_softmax_kernel<float><<<(unsigned)rows, 256, 0, st>>>(s, (float*)p, rows_per_head, keys, first_pos, scale, window, key0, sink, split)));
   return (int)cudaGetLastError();
 }
 

@@ -78,7 +78,7 @@ def lib() -> ctypes.CDLL:
     h.hyb_softcap.argtypes = [vp, vp, i64, f32, i32, vp]
     h.hyb_latent_append.argtypes = [vp, i64, vp, i64, vp, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp]
     h.hyb_latent_attn.argtypes = [vp, vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp, vp, i32, vp]
-    h.hyb_causal_softmax.argtypes = [vp, vp, i64, i32, i32, i32, f32, i32, i32, i32, i32, vp]
+    h.hyb_causal_softmax.argtypes = [vp, vp, i64, i32, i32, i32, f32, i32, i32, i32, i32, i32, vp]
     h.hyb_conv_silu.argtypes = [vp, i64, vp, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, vp]
     h.hyb_gated_recurrence.argtypes = [ctypes.POINTER(_RecArgs), i32, i32, i32, i32, vp, vp, vp, vp]
     _lib = h
@@ -417,11 +417,14 @@ def latent_attn(qlat: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, plan: 
 
 
 def causal_softmax(scores: torch.Tensor, first_pos: int, scale: float, out_dtype: torch.dtype, window: int = 0,
-                   key0: int = 0, sink: bool = False) -> torch.Tensor:
+                   key0: int = 0, sink: bool = False, split: bool = False) -> torch.Tensor:
     """``softmax(scale * scores)`` over the visible keys of fp32 ``scores [heads, rows, keys]``: row ``i`` is position
     ``first_pos + i``, column ``j`` is position ``key0 + j``; a key is visible when it is not later than the row and,
     with ``window > 0``, fewer than ``window`` positions back.  Hidden keys get probability 0.  Result in ``out_dtype``.
-    ``sink``: the denominator gains one slot of score zero that has no value, ``p_j = e^{s_j} / (1 + sum_k e^{s_k})``."""
+    ``sink``: the denominator gains one slot of score zero that has no value, ``p_j = e^{s_j} / (1 + sum_k e^{s_k})``.
+    ``split``: the result is ``[heads, rows, 2 * keys]``: the weights rounded to ``out_dtype`` and, behind them, what the
+    rounding dropped (``p - round(p)``, rounded again).  A product with the values stacked twice then sums the weights to
+    twice the mantissa of ``out_dtype`` on the tensor cores."""
     Hh, n, keys = scores.shape
     if not scores.is_cuda:
         j = key0 + torch.arange(keys)
@@ -432,12 +435,16 @@ def causal_softmax(scores: torch.Tensor, first_pos: int, scale: float, out_dtype
         sc = (scores.float() * scale).masked_fill(hidden, float("-inf"))
         if sink:
             sc = torch.cat((sc, sc.new_zeros(Hh, n, 1)), -1)
-        return torch.softmax(sc, -1)[..., :keys].to(out_dtype)
+        pr = torch.softmax(sc, -1)[..., :keys]
+        if split:
+            hi = pr.to(out_dtype)
+            return torch.cat((hi, (pr - hi.float()).to(out_dtype)), -1)
+        return pr.to(out_dtype)
     if scores.dtype != torch.float32 or not scores.is_contiguous():
         raise HybridOpsError("scores are dense fp32")
-    p = torch.empty(Hh, n, keys, device=scores.device, dtype=out_dtype)
+    p = torch.empty(Hh, n, 2 * keys if split else keys, device=scores.device, dtype=out_dtype)
     _check(lib().hyb_causal_softmax(scores.data_ptr(), p.data_ptr(), Hh * n, n, keys, int(first_pos), float(scale),
-                                    int(window), int(key0), int(bool(sink)), _dt(p), _st()), "causal_softmax")
+                                    int(window), int(key0), int(bool(sink)), int(bool(split)), _dt(p), _st()), "causal_softmax")
     return p
 
 

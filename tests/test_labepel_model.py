@@ -202,6 +202,10 @@ def test_softmax_with_a_sink(dev):
     assert got[1, 4].sum() < 1e-6 and abs(got[2, 8].sum() - 1.0) < 1e-5
     plain = H.causal_softmax(s.to(device).contiguous(), first, scale, torch.float32, key0=key0).cpu()
     assert torch.allclose(plain.sum(-1), torch.ones(3, 9), atol=1e-5) and (got.sum(-1) <= 1.0 + 1e-6).all() and got.sum(-1).mean() < 0.97
+    # the weights as two halves of the 16-bit type: together they carry 16 bits of mantissa
+    halves = H.causal_softmax(s.to(device).contiguous(), first, scale, torch.bfloat16, key0=key0, sink=True, split=True).double().cpu()
+    assert halves.shape == (3, 9, 28)
+    assert ((halves[..., :14] + halves[..., 14:] - want).abs() <= want * 2.0 ** -15 + 1e-30).all()
 
 
 def test_router_softmax_over_the_chosen_lower_index_on_ties():
@@ -309,6 +313,26 @@ def test_unequal_batch_equals_each_alone_and_slots_are_reused(dev, lengths):
     assert not r.pool.length
     t = toks(75, seed=99)  # freed slots serve a new request: nothing of the old cache shows
     close(r.step([("new", t)], all_rows(75)), oracle_logits(d, m, t), dev, "reused slot")
+
+
+@pytest.mark.parametrize("dev", DEVICES)
+def test_pool_grows_while_requests_are_held(dev):
+    """Two requests decode (on the GPU: through a captured step), three more arrive as a batch of their own and the
+    pool has to grow: the new ones start clean and the old ones go on from the state they had."""
+    d, m = build(FULL, dev)
+    seqs = [toks(n, seed=20 + i) for i, n in enumerate((80, 66, 140, 71, 5))]
+    want = [oracle_logits(d, m, t) for t in seqs]
+    r = HybridRunner(m, 192, n_slots=2)
+    r.step([(0, seqs[0][:70]), (1, seqs[1][:60])])
+    for s in range(3):  # the third one-token step of this batch size runs as a captured graph on the GPU
+        out = r.step([(0, [seqs[0][70 + s]]), (1, [seqs[1][60 + s]])])
+        close(out, torch.stack((want[0][70 + s], want[1][60 + s])), dev, f"before growth {s}")
+    out = r.step([(i, seqs[i]) for i in (2, 3, 4)])
+    assert r.pool.n_slots >= 5
+    close(out, torch.stack([want[i][-1] for i in (2, 3, 4)]), dev, "arrivals")
+    for s in range(3, 6):
+        out = r.step([(0, [seqs[0][70 + s]]), (1, [seqs[1][60 + s]])])
+        close(out, torch.stack((want[0][70 + s], want[1][60 + s])), dev, f"after growth {s}")
 
 
 @pytest.mark.parametrize("dev", DEVICES)
