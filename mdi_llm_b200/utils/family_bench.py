@@ -257,8 +257,8 @@ def _labepel_kernels(model: Any, T: int, batch: int) -> List[Dict[str, Any]]:
                 2.0 * N * (Hh * (D + 2 * V) + G * (D + V)), 2.0 * Hh * pairs * (D + V))
             nb = min(N, W) if W else min(N, att.query_block)
             s32 = torch.randn(max(1, N // nb) * Hh, nb, nb, device=dev)
-            ms = _time(lambda: H.causal_softmax(s32, 0, att.scale, torch.float32, sink=att.sink), 5, 3, flush)
-            rec("causal_softmax[sink, fp32 weights]", "causal_softmax[window]", phase, ms, s32.numel() * 8.0, 0.0)
+            ms = _time(lambda: H.causal_softmax(s32, 0, att.scale, dt, sink=att.sink, split=True), 5, 3, flush)
+            rec("causal_softmax[sink, split weights]", "causal_softmax[window]", phase, ms, s32.numel() * 8.0, 0.0)
             del s32
         else:
             ms = _time(lambda: H.window_attn(q, g, cache, plan, Hh, G, D, V, att.scale, W, mask=att.mask_kind, sink=att.sink),
