@@ -355,6 +355,7 @@ __global__ void latent_combine_kernel(const float* __restrict__ part_acc, const 
 // sink != 0: one more slot of score zero joins the denominator (it has no value): p_j = e^{s_j} / (1 + sum e^{s_k}).
 // split != 0: a row of p is 2 * keys wide: the weights rounded to T, and behind them the remainders (weight minus its
 // rounding) rounded to T, so that a matrix product with the values stacked twice sums the weights to 16 mantissa bits.
+#define CS_CACHE 8  // scores a thread keeps in registers: rows of up to 8 * 256 keys are read once
 template <typename T>
 __global__ void causal_softmax_kernel(const float* __restrict__ s, T* __restrict__ p, int rows_per_head, int keys,
                                       int first_pos, float scale, int window, int key0, int sink, int split) {
@@ -365,9 +366,58 @@ __global__ void causal_softmax_kernel(const float* __restrict__ s, T* __restrict
   int vis = max(0, min(keys, pos - key0 + 1));
   int lo = window > 0 ? max(0, pos - window + 1 - key0) : 0;
   const float* src = s + row * keys;
-  T* dst = p + row * keys;
+  T* dst = p + row * (split ? 2 * (size_t)keys : (size_t)keys);
+  bool cached = keys <= CS_CACHE * (int)blockDim.x;  // the same for every thread of the block
+  float v[CS_CACHE];
   float m = -INFINITY;
-  for (int j = lo + threadIdx.x; j < vis; j += blockDim.x) m = fmaxf(m, src[j]);
+  if (cached && (keys & 7) == 0) {
+    // rows of a multiple of 8 keys: a thread owns 8 neighbouring keys, read with two 16-byte loads and written with
+    // one (bf16) or two (fp32) 16-byte stores per output; threads past the row's end only take part in the sums
+    int j0 = threadIdx.x * 8;
+    bool mine = j0 < keys;
+    if (mine) load8(src + j0, v);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      int j = j0 + c;
+      if (!(mine && j >= lo && j < vis)) v[c] = -INFINITY;
+      m = fmaxf(m, v[c]);
+    }
+    m = warp_max(m);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    m = -INFINITY;
+    for (int w = 0; w < (blockDim.x + 31) / 32; ++w) m = fmaxf(m, red[w]);
+    if (sink) m = fmaxf(m, 0.f);
+    float sum = 0.f;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      v[c] = v[c] == -INFINITY ? 0.f : expf((v[c] - m) * scale);
+      sum += v[c];
+    }
+    sum = block_sum(sum, red);
+    if (sink) sum += expf(-m * scale);
+    float inv = 1.f / sum;
+    if (!mine) return;
+    float rest[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      v[c] = v[c] == 0.f ? 0.f : v[c] * inv;
+      rest[c] = v[c] - to_f(from_f<T>(v[c]));
+    }
+    store8(dst + j0, v);
+    if (split) store8(dst + keys + j0, rest);
+    return;
+  }
+  if (cached) {
+#pragma unroll
+    for (int c = 0; c < CS_CACHE; ++c) {
+      int j = threadIdx.x + c * blockDim.x;
+      v[c] = j >= lo && j < vis ? src[j] : -INFINITY;
+      m = fmaxf(m, v[c]);
+    }
+  } else {
+    for (int j = lo + threadIdx.x; j < vis; j += blockDim.x) m = fmaxf(m, src[j]);
+  }
   m = warp_max(m);
   __syncthreads();
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
@@ -376,22 +426,37 @@ __global__ void causal_softmax_kernel(const float* __restrict__ s, T* __restrict
   for (int w = 0; w < (blockDim.x + 31) / 32; ++w) m = fmaxf(m, red[w]);
   if (sink) m = fmaxf(m, 0.f);  // scale > 0: the shift that keeps every exponent <= 0
   float sum = 0.f;
-  for (int j = lo + threadIdx.x; j < vis; j += blockDim.x) sum += expf((src[j] - m) * scale);
+  if (cached) {
+#pragma unroll
+    for (int c = 0; c < CS_CACHE; ++c) {
+      v[c] = v[c] == -INFINITY ? 0.f : expf((v[c] - m) * scale);  // hidden keys: weight zero
+      sum += v[c];
+    }
+  } else {
+    for (int j = lo + threadIdx.x; j < vis; j += blockDim.x) sum += expf((src[j] - m) * scale);
+  }
   sum = block_sum(sum, red);
   if (sink) sum += expf(-m * scale);
   float inv = 1.f / sum;
-  if (split) {
-    dst = p + row * 2 * keys;
-    for (int j = threadIdx.x; j < keys; j += blockDim.x) {
-      float v = j >= lo && j < vis ? expf((src[j] - m) * scale) * inv : 0.f;
-      T hi = from_f<T>(v);
-      dst[j] = hi;
-      dst[keys + j] = from_f<T>(v - to_f(hi));
+  if (cached) {
+#pragma unroll
+    for (int c = 0; c < CS_CACHE; ++c) {
+      int j = threadIdx.x + c * blockDim.x;
+      if (j < keys) {
+        float w = v[c] == 0.f ? 0.f : v[c] * inv;  // a row without a visible key and without a sink: inv is infinite
+        T hi = from_f<T>(w);
+        dst[j] = hi;
+        if (split) dst[keys + j] = from_f<T>(w - to_f(hi));
+      }
     }
     return;
   }
-  for (int j = threadIdx.x; j < keys; j += blockDim.x)
-    dst[j] = from_f<T>(j >= lo && j < vis ? expf((src[j] - m) * scale) * inv : 0.f);
+  for (int j = threadIdx.x; j < keys; j += blockDim.x) {
+    float w = j >= lo && j < vis ? expf((src[j] - m) * scale) * inv : 0.f;
+    T hi = from_f<T>(w);
+    dst[j] = hi;
+    if (split) dst[keys + j] = from_f<T>(w - to_f(hi));
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -886,8 +951,12 @@ int hyb_causal_softmax(const float* s, void* p, long long rows, int rows_per_hea
                        int window, int key0, int sink, int split, int dt, cudaStream_t st) {
   if (rows == 0) return 0;
   if (scale <= 0.f) return -3;  // the row maximum is taken before scaling
-  HYB_DISPATCH(dt, (causal_softmax_kernel<bf16><<<(unsigned)rows, 256, 0, st>>>(s, (bf16*)p, rows_per_head, keys, first_pos, scale, window, key0, sink, split)),
-               (causal_softmax_kernel<float><<<(unsigned)rows, 256, 0, st>>>(s, (float*)p, rows_per_head, keys, first_pos, scale, window, key0, sink, split)));
+  // rows of up to 2048 keys in multiples of 8: 8 keys per thread, so only as many warps as the row needs
+  int th = (keys & 7) == 0 && keys <= 2048 ? ((keys / 8 + 31) / 32) * 32 : 256;
+  if (th != 256 || ((keys & 7) == 0 && keys <= 2048))
+    if (((uintptr_t)s | (uintptr_t)p) & 15) return -4;  // the 16-byte loads and stores of that form
+  HYB_DISPATCH(dt, (causal_softmax_kernel<bf16><<<(unsigned)rows, th, 0, st>>>(s, (bf16*)p, rows_per_head, keys, first_pos, scale, window, key0, sink, split)),
+               (causal_softmax_kernel<float><<<(unsigned)rows, th, 0, st>>>(s, (float*)p, rows_per_head, keys, first_pos, scale, window, key0, sink, split)));
   return (int)cudaGetLastError();
 }
 

@@ -208,6 +208,25 @@ def test_softmax_with_a_sink(dev):
     assert ((halves[..., :14] + halves[..., 14:] - want).abs() <= want * 2.0 ** -15 + 1e-30).all()
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("keys", [37, 40, 1032, 2048, 2100],  # rows kept in registers (eight neighbours per thread when
+                         ids=["odd", "short", "five_warps", "register_limit", "long"])  # they come in eights), and rows that are not
+@pytest.mark.parametrize("sink", [False, True])
+def test_softmax_kernel_matches_its_plain_form_for_short_and_long_rows(keys, sink):
+    g = torch.Generator().manual_seed(keys)
+    s = torch.randn(2, 6, keys, generator=g) * 3.0
+    first, key0, window = keys - 9, 4, 37
+    for kw in ({}, {"window": window}):
+        want = H.causal_softmax(s, first, 0.5, torch.float32, key0=key0, sink=sink, **kw)
+        got = H.causal_softmax(s.cuda(), first, 0.5, torch.float32, key0=key0, sink=sink, **kw).cpu()
+        assert (got - want).abs().max() < 1e-6 and torch.equal(got == 0, want == 0)
+        halves = H.causal_softmax(s.cuda(), first, 0.5, torch.bfloat16, key0=key0, sink=sink, split=True, **kw).float().cpu()
+        assert ((halves[..., :keys] + halves[..., keys:] - want).abs() <= want * 2.0 ** -15 + 1e-30).all()
+    # rows that see no key at all (they lie before the first column): zeros, not NaN
+    got = H.causal_softmax(s.cuda(), 0, 0.5, torch.float32, key0=3, sink=sink).cpu()
+    assert torch.equal(got[:, :3], torch.zeros(2, 3, keys)) and not got.isnan().any()
+
+
 def test_router_softmax_over_the_chosen_lower_index_on_ties():
     z = torch.tensor([[0.1, 2.0, 2.0, -1.0], [3.0, -2.0, 0.5, 0.5]])
     idx, wt = H.router_topk(z, 3, "softmax")
