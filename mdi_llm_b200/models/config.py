@@ -213,25 +213,36 @@ MIXER_KEYS = {
     "gla": ("heads", "dim", "vdim", "tau"),
     "channel_delta": ("heads", "kv_heads", "dim", "vdim", "conv"),
     "attention": ("heads", "kv_heads", "dim", "vdim", "scale"),
+    "lightning": ("heads", "dim", "vdim", "decay"),
 }
 
 # What an architecture of the family fixes beyond its config.json: the shape of a block ("sandwich": norms before and
 # after each sublayer; "prenorm": one norm before, the sublayer output times ``residual_mult`` added; "parallel": one
 # norm whose output both the mixer and the feed-forward read, their outputs summed into the residual), the kind of
+# "postnorm": the sublayer reads the residual stream itself and its *output* is normed before it is added),
 # its norms (``norm_offset`` is added to every block-level norm weight: 1 for weights stored as deviations from one),
 # whether the output head is the embedding table or a tensor of its own, whether a learned position vector joins the
 # token embedding (``positions``), whether each branch of a block has a learned scale per channel (``layer_scale``),
 # and the variant of the grouped-query attention mixer and of the mixture of experts:
 #   attention: mask "window" (the last mask.size positions) | "chunk" (the query's own block of mask.size positions);
-#              sink (a zero-score slot in the softmax denominator); qk_norm "unit" (divide by the RMS) | "weight" (RMS
-#              norm with a learned weight per entry, shared by the heads); bias on q, k, v; gate "head" | "channel";
+#              sink: True (a zero-score slot in the softmax denominator) | "learned" (its score is a tensor, one number
+#              per head); qk_norm "unit" (divide by the RMS) | "weight" (RMS norm with a learned weight per entry,
+#              shared by the heads) | "full" (RMS norm over the WHOLE projection, all heads at once, with a weight per
+#              entry, BEFORE the rotation); bias on q, k, v; gate "head" | "channel";
 #              p32 (the prompt form sums the values with softmax weights of more than the activation type's mantissa:
 #              fp32 weights, or with 16-bit activations their rounding and its remainder as two 16-bit operands)
-#   moe:       router "sigmoid" (independent scores) | "softmax" (over the chosen logits); router_bias; expert "relu2"
-#              (down relu(up x)^2, the score scales the input) | "gated_silu" (down (silu(gate x) * up x), the score
-#              weighs the output); a ``shared`` always-on expert is read from the layer's mlp entry
+#   moe:       router "sigmoid" (independent scores) | "softmax" (over the chosen logits) | "softmax_all" (scores are
+#              the softmax over all router outputs, the choice goes by score + a ``correction`` tensor, the weights are
+#              the chosen scores divided by their sum); router_bias; expert "relu2" (down relu(up x)^2, the score scales
+#              the input) | "gated_silu" (down (silu(gate x) * up x), the score weighs the output) | "clamped" (gate and
+#              up clamped by the entry's ``limit``, g sigmoid(1.702 g) (u + 1)); a ``shared`` always-on expert is read
+#              from the layer's mlp entry; shared_gate: the shared expert's output is weighed by one sigmoid per token
+#   dense_act: activation of a dense feed-forward, "gelu" (erf) | "relu2"
+# Per layer, an attention mixer may also name ``softcap`` (scores pass through cap * tanh(score / cap)) and
+# ``kv_from: j`` (no key/value projections: it reads the keys and values layer j cached); a mixture of experts may name
+# ``router.identity`` (that many extra router outputs whose "expert" returns its input).
 _ATTENTION_DEFAULT = {"mask": "window", "sink": False, "qk_norm": "unit", "bias": False, "gate": "head", "p32": False}
-_MOE_DEFAULT = {"router": "sigmoid", "router_bias": False, "expert": "relu2"}
+_MOE_DEFAULT = {"router": "sigmoid", "router_bias": False, "expert": "relu2", "shared_gate": False}
 ARCHITECTURE_TRAITS = {
     "Badapel": {"block": "sandwich", "norm": "layer", "tied_head": True},
     "Vudelix": {"block": "prenorm", "norm": "rms", "tied_head": False},
@@ -239,6 +250,9 @@ ARCHITECTURE_TRAITS = {
                 "layer_scale": True,
                 "attention": {"mask": "chunk", "sink": True, "qk_norm": "weight", "bias": True, "gate": "channel", "p32": True},
                 "moe": {"router": "softmax", "router_bias": True, "expert": "gated_silu"}},
+    "Zudovik": {"block": "postnorm", "norm": "rms", "tied_head": False, "dense_act": "relu2",
+                "attention": {"mask": "window", "sink": "learned", "qk_norm": "full", "bias": True, "gate": "head", "p32": True},
+                "moe": {"router": "softmax_all", "expert": "clamped", "shared_gate": True}},
 }
 FF_KINDS = ("dense", "moe")
 
@@ -259,7 +273,7 @@ class HybridConfig:
     ``block``, ``norm``, ``norm_offset``, ``tied_head``, ``positions``, ``layer_scale`` and the mixer variants
     ``attention`` / ``moe`` come from :data:`ARCHITECTURE_TRAITS` unless given.  ``max_positions`` is the length of the
     learned position table (``positions = "learned"``).  A mixture of experts may name a ``shared`` expert
-    (``{"ff": n}``) that every token uses.
+    (``{"ff": n}``) that every token uses.  ``embed_scale`` (``embedding.scale``) multiplies the token embedding.
     """
 
     architecture: str = "Badapel"
@@ -281,6 +295,8 @@ class HybridConfig:
     layer_scale: Optional[bool] = None
     attention: Optional[dict] = None
     moe: Optional[dict] = None
+    embed_scale: float = 1.0
+    dense_act: str = ""
 
     def __post_init__(self) -> None:
         traits = ARCHITECTURE_TRAITS.get(self.architecture, ARCHITECTURE_TRAITS["Badapel"])
@@ -295,13 +311,17 @@ class HybridConfig:
             self.layer_scale = bool(traits.get("layer_scale", False))
         self.attention = {**_ATTENTION_DEFAULT, **traits.get("attention", {}), **(self.attention or {})}
         self.moe = {**_MOE_DEFAULT, **traits.get("moe", {}), **(self.moe or {})}
-        if self.block not in ("sandwich", "prenorm", "parallel") or self.norm not in ("layer", "rms"):
+        self.dense_act = self.dense_act or traits.get("dense_act", "gelu")
+        if self.dense_act not in ("gelu", "relu2"):
+            raise ValueError(f"unknown dense feed-forward activation {self.dense_act!r}")
+        if self.block not in ("sandwich", "prenorm", "parallel", "postnorm") or self.norm not in ("layer", "rms"):
             raise ValueError(f"unknown block {self.block!r} or norm {self.norm!r}")
         if self.positions not in ("none", "learned") or (self.positions == "learned" and self.max_positions < 1):
             raise ValueError("learned positions need max_positions >= 1")
-        if self.attention["mask"] not in ("window", "chunk") or self.attention["qk_norm"] not in ("unit", "weight") \
-                or self.attention["gate"] not in ("head", "channel") or self.moe["router"] not in ("sigmoid", "softmax") \
-                or self.moe["expert"] not in ("relu2", "gated_silu"):
+        if self.attention["mask"] not in ("window", "chunk") or self.attention["qk_norm"] not in ("unit", "weight", "full") \
+                or self.attention["gate"] not in ("head", "channel") or self.attention["sink"] not in (False, True, "learned") \
+                or self.moe["router"] not in ("sigmoid", "softmax", "softmax_all") \
+                or self.moe["expert"] not in ("relu2", "gated_silu", "clamped"):
             raise ValueError(f"unknown attention or mixture-of-experts variant: {self.attention} {self.moe}")
         if self.token_side is not None and int(self.token_side.get("dim", 0)) <= 0:
             raise ValueError("token_side needs a positive dim")
@@ -319,13 +339,27 @@ class HybridConfig:
                 raise ValueError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
             if mlp is not None and mlp["kind"] == "moe":
                 r = mlp.get("router", {})
-                if not (1 <= int(r.get("top", 0)) <= int(r.get("experts", 0))) or int(mlp.get("expert", {}).get("ff", 0)) <= 0:
+                if not (1 <= int(r.get("top", 0)) <= int(r.get("experts", 0)) + int(r.get("identity", 0) or 0)) \
+                        or int(r.get("experts", 0)) < 1 or int(mlp.get("expert", {}).get("ff", 0)) <= 0:
                     raise ValueError(f"layer {i}: a mixture of experts needs expert.ff and 1 <= router.top <= router.experts")
                 if mlp.get("shared") and int(mlp["shared"].get("ff", 0)) <= 0:
                     raise ValueError(f"layer {i}: a shared expert needs a positive ff")
+                if int(r.get("identity", 0) or 0) < 0 or int(r["top"]) > int(r["experts"]) + int(r.get("identity", 0) or 0):
+                    raise ValueError(f"layer {i}: router.identity is a count of extra router outputs")
+                if self.moe["expert"] == "clamped" and ("limit" not in mlp["expert"] or (mlp.get("shared") and "limit" not in mlp["shared"])):
+                    raise ValueError(f"layer {i}: clamped experts need a limit")
             m = spec["mixer"]
             if kind in ("attention", "channel_delta") and int(m["heads"]) % int(m["kv_heads"]):
                 raise ValueError(f"layer {i}: heads must be a multiple of kv_heads")
+            if kind == "lightning" and len(m["decay"]) != int(m["heads"]):
+                raise ValueError(f"layer {i}: one decay per head")
+            if kind == "attention" and m.get("kv_from") is not None:
+                j = int(m["kv_from"])
+                src = self.layers[j] if 0 <= j < i else None
+                if src is None or src.get("type") != "attention" or src["mixer"].get("kv_from") is not None:
+                    raise ValueError(f"layer {i}: kv_from names an earlier attention layer with projections of its own")
+                if any(src["mixer"][k] != m[k] for k in ("kv_heads", "dim", "vdim")) or src["mixer"].get("rot") != m.get("rot"):
+                    raise ValueError(f"layer {i}: kv_from needs the source layer's kv_heads, dim, vdim and rotation")
         if self.loop is not None:
             a, b, t = self.loop["start"], self.loop["stop"], self.loop["times"]
             if not (0 <= a < b <= len(self.layers)) or t < 1:
@@ -364,7 +398,8 @@ class HybridConfig:
                    logit_softcap=float(d.get("logit_softcap") or 0.0), name=d.get("name", ""),
                    residual_mult=float(d.get("residual_mult", 1.0)),
                    token_side=dict(d["token_side"]) if d.get("token_side") else None,
-                   max_positions=int(d.get("max_positions") or 0))
+                   max_positions=int(d.get("max_positions") or 0),
+                   embed_scale=float((d.get("embedding") or {}).get("scale", 1.0)))
 
     @classmethod
     def from_file(cls, path: Union[str, Path]) -> "HybridConfig":
@@ -386,6 +421,8 @@ class HybridConfig:
             out["token_side"] = self.token_side
         if self.max_positions:
             out["max_positions"] = self.max_positions
+        if self.embed_scale != 1.0:
+            out["embedding"] = {"scale": self.embed_scale}
         return out
 
     def save(self, checkpoint_dir: Union[str, Path]) -> Path:

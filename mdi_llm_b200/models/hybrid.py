@@ -14,10 +14,14 @@ Mixers (all written against the packed-batch operations of :mod:`mdi_llm_b200.op
   interleaved rotary positions (optionally stretched by wavelength), weight-free RMS norm of q and k after the
   rotation, and one sigmoid output gate per head.
 
+* :class:`LightningAttention` — ``S_t = decay_h S_(t-1) + k_t v_t^T`` with one fixed decay per head, SiLU on q, k, v,
+  an RMS norm over all heads' read-outs together and a sigmoid gate per channel.
+
 Feed-forwards: :class:`DenseFF` and :class:`MoEFF` (sigmoid router, top-k, the score scales the expert's *input*).
 
-A layer is a *sandwich* block (``x += norm_b(f(norm_a(x)))`` for the mixer and again for the feed-forward) or a
-*pre-norm* block (``x += m f(norm(x))``, optionally followed by a gated per-layer token embedding), chosen by the
+A layer is a *sandwich* block (``x += norm_b(f(norm_a(x)))`` for the mixer and again for the feed-forward), a
+*pre-norm* block (``x += m f(norm(x))``, optionally followed by a gated per-layer token embedding), a *parallel* block
+or a *post-norm* block (``x += norm(f(x))``: the sublayer reads the residual stream itself), chosen by the
 architecture (``config.block``), with the residual stream kept in fp32.  A span of layers may be looped; each pass owns its own state and starts by
 mixing the embedding output back in.  State lives in a :class:`StatePool` — slots like the KV pool of the
 transformer family (``models/gpt.py:KVPool``), one entry per *layer run*.
@@ -35,8 +39,8 @@ import torch.nn as nn
 from ..ops import hybrid as H
 from .config import HybridConfig
 
-__all__ = ["HybridLM", "StatePool", "SandwichBlock", "PreNormBlock", "ParallelBlock", "LatentAttention", "GatedLinearAttention",
-           "ChannelDelta", "WindowAttention", "DenseFF", "GatedFF", "MoEFF", "read_safetensors", "write_safetensors", "load_hybrid"]
+__all__ = ["HybridLM", "StatePool", "SandwichBlock", "PreNormBlock", "ParallelBlock", "PostNormBlock", "LatentAttention",
+           "GatedLinearAttention", "ChannelDelta", "WindowAttention", "LightningAttention", "DenseFF", "GatedFF", "MoEFF", "read_safetensors", "write_safetensors", "load_hybrid"]
 
 _ST_DTYPES = {"BF16": torch.bfloat16, "F32": torch.float32, "F16": torch.float16, "I32": torch.int32, "I64": torch.int64}
 
@@ -86,7 +90,9 @@ class StatePool:
     of a recurrent layer owns ``state [slots, heads, dim, vdim]`` in fp32 and, with a short convolution,
     ``conv [slots, taps - 1, channels]``.  ``alloc`` hands out a slot with zeroed recurrent and convolution state
     (attention rows need no clearing: a row is written before any query can see it); ``free`` returns it.
-    The pool grows (doubling, contents kept) when more slots are asked for than it has.
+    The pool grows (doubling, contents kept) when more slots are asked for than it has.  A run of an attention layer
+    that names ``kv_from`` owns nothing: its ``cache`` entry IS the cache of the latest earlier run of the layer it
+    names (the same tensor), which that run has already extended by the step's tokens when this one reads it.
     """
 
     def __init__(self, config: HybridConfig, n_slots: int, max_seq_length: int, device: torch.device, dtype: torch.dtype) -> None:
@@ -101,6 +107,8 @@ class StatePool:
         m = spec["mixer"]
         if spec["type"] == "latent_attention":
             return {"cache": ((self.max_seq_length, m["kv_rank"] + m["rot_dim"]), self.dtype)}
+        if spec["type"] == "attention" and m.get("kv_from") is not None:
+            return {}
         if spec["type"] == "attention":  # one row per position: the kv_heads keys, then the kv_heads values
             return {"cache": ((self.max_seq_length, m["kv_heads"] * (m["dim"] + m["vdim"])), self.dtype)}
         out = {"state": ((m["heads"], m["dim"], m["vdim"]), torch.float32)}
@@ -116,6 +124,12 @@ class StatePool:
                 if key in run:
                     new[: self.n_slots] = run[key]
                 run[key] = new
+        order = self.config.layer_runs()
+        for r, (li, _) in enumerate(order):
+            src = self.config.layers[li]["mixer"].get("kv_from") if self.config.layers[li]["type"] == "attention" else None
+            if src is not None:
+                owner = max(j for j in range(r) if order[j][0] == int(src))
+                self.runs[r]["cache"] = self.runs[owner]["cache"]
         self.free_slots += list(range(self.n_slots, n_slots))
         self.n_slots = n_slots
 
@@ -138,7 +152,8 @@ class StatePool:
 
     @property
     def nbytes(self) -> int:
-        return sum(t.numel() * t.element_size() for run in self.runs for t in run.values())
+        own = {t.data_ptr(): t for run in self.runs for t in run.values()}  # a borrowed cache counts once
+        return sum(t.numel() * t.element_size() for t in own.values())
 
 
 # =============================================================================================
@@ -308,7 +323,12 @@ class WindowAttention(nn.Module, _Fused):
     zero-score sink; the output gate is one sigmoid per head or per channel.  A layer whose mixer entry says
     ``v_mix`` blends its values with those the first such layer computed for the same token,
     ``v <- (1 - lam) v + lam v_first`` (``lam`` the layer's ``vmix`` scalar; the first such layer keeps its own), and
-    caches the blend."""
+    caches the blend.
+
+    Further variants: ``qk_norm="full"`` norms the whole q projection (all heads at once) and the whole k projection
+    with a weight per entry BEFORE the rotation; ``sink="learned"`` gives the sink a score per head (tensor ``sink``);
+    a mixer entry may name ``softcap`` (scores become ``cap tanh(score / cap)`` after the scale) and ``kv_from``: the
+    layer then has no key/value projections, prepares only its queries and reads the cache of the layer it names."""
 
     expand_from = 64   # a step whose every sequence brings at least this many tokens runs as batched matrix products
     query_block = 1024  # query rows per band
@@ -322,22 +342,41 @@ class WindowAttention(nn.Module, _Fused):
         self.window = int((m.get("mask") or {}).get("size", 0) or 0)
         self.mask_kind, self.sink, self.p32 = str(t["mask"]), bool(t["sink"]), bool(t["p32"])
         self.v_mix = bool(m.get("v_mix"))
+        self.softcap = float(m.get("softcap") or 0.0)
+        self.borrows = m.get("kv_from") is not None
+        self.full_norm = t["qk_norm"] == "full"
+        if self.borrows and (self.v_mix or not self.full_norm):
+            raise ValueError("kv_from is implemented for the full-projection q/k norm, without value mixing")
         rot = m.get("rot") or {}
         self.nrot, self.rot_base, self.rot_scaling = int(rot.get("dims", 0)), float(rot.get("base", 10000.0)), rot.get("scaling")
         if self.nrot > self.D or self.nrot % 2:
             raise ValueError("rot.dims must be even and at most dim")
         Hh, G, D, V = self.H, self.G, self.D, self.V
-        self.q, self.k, self.v = _param(Hh * D, width), _param(G * D, width), _param(G * V, width)
+        self.q = _param(Hh * D, width)
         self.g, self.o = _param(Hh if t["gate"] == "head" else Hh * V, width), _param(width, Hh * V)
-        self.tensor_names = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o"}
+        self.tensor_names = {"q": "q", "g": "g", "o": "o"}
         self.has_bias = bool(t["bias"])
         if self.has_bias:
-            self.q_b, self.k_b, self.v_b = _param(Hh * D), _param(G * D), _param(G * V)
-            self.tensor_names.update({"q.b": "q_b", "k.b": "k_b", "v.b": "v_b"})
+            self.q_b = _param(Hh * D)
+            self.tensor_names["q.b"] = "q_b"
         self.q_norm = self.k_norm = None
-        if t["qk_norm"] == "weight":
-            self.q_norm, self.k_norm = _param(D), _param(D)
-            self.tensor_names.update({"q.norm": "q_norm", "k.norm": "k_norm"})
+        if t["qk_norm"] in ("weight", "full"):
+            self.q_norm = _param(Hh * D if self.full_norm else D)
+            self.tensor_names["q.norm"] = "q_norm"
+        if not self.borrows:
+            self.k, self.v = _param(G * D, width), _param(G * V, width)
+            self.tensor_names.update({"k": "k", "v": "v"})
+            if self.has_bias:
+                self.k_b, self.v_b = _param(G * D), _param(G * V)
+                self.tensor_names.update({"k.b": "k_b", "v.b": "v_b"})
+            if self.q_norm is not None:
+                self.k_norm = _param(G * D if self.full_norm else D)
+                self.tensor_names["k.norm"] = "k_norm"
+        self.sink_w = None
+        if t["sink"] == "learned":
+            self.sink_w = _param(Hh)
+            self.tensor_names["sink"] = "sink_w"
+        self.sink32: Optional[torch.Tensor] = None
         if self.v_mix:
             self.vmix = nn.Parameter(torch.empty(()), requires_grad=False)
             self.tensor_names["vmix"] = "vmix"
@@ -345,9 +384,12 @@ class WindowAttention(nn.Module, _Fused):
         self.b_in: Optional[torch.Tensor] = None
 
     def finalize(self) -> None:
-        self.fuse(("q", "k", "v", "g"))
+        self.fuse(("q", "g") if self.borrows else ("q", "k", "v", "g"))
         if self.has_bias:  # one bias vector for the fused projection; the gate has none
-            self.b_in = torch.cat((self.q_b.data, self.k_b.data, self.v_b.data, torch.zeros_like(self.g.data[:, 0]))).contiguous()
+            kv = () if self.borrows else (self.k_b.data, self.v_b.data)
+            self.b_in = torch.cat((self.q_b.data, *kv, torch.zeros_like(self.g.data[:, 0]))).contiguous()
+        if self.sink_w is not None:
+            self.sink32 = self.sink_w.data.float().contiguous()
         if self.v_mix:
             self.lam = self.vmix.data.reshape(1).contiguous()
         if self.nrot:
@@ -358,7 +400,13 @@ class WindowAttention(nn.Module, _Fused):
         """``p``: the fused input projection of ``h`` when the caller has already computed it."""
         if p is None:
             p = H.linear(h, self.w_in, self.b_in)
-        q, g, v = self.col(p, "q"), self.col(p, "g"), self.col(p, "v")
+        q, g = self.col(p, "q"), self.col(p, "g")
+        if self.full_norm:
+            k, v = (None, None) if self.borrows else (self.col(p, "k"), self.col(p, "v"))
+            H.full_norm_append(q, k, v, self.inv_freq, st["cache"], plan, self.H, self.G, self.D, self.V, self.nrot,
+                               self.eps, self.q_norm, self.k_norm)
+            return self._attend(q, g, st["cache"], plan)
+        v = self.col(p, "v")
         v_first = lam = None
         if self.v_mix:
             v_first = plan.shared.get("v_first")
@@ -370,12 +418,16 @@ class WindowAttention(nn.Module, _Fused):
                 lam = self.lam
         H.window_append(q, self.col(p, "k"), v, self.inv_freq, st["cache"], plan, self.H, self.G, self.D,
                         self.V, self.nrot, self.eps, self.q_norm, self.k_norm, v_first, lam)
+        return self._attend(q, g, st["cache"], plan)
+
+    def _attend(self, q: torch.Tensor, g: torch.Tensor, cache: torch.Tensor, plan: H.BatchPlan) -> torch.Tensor:
+        """Prepared queries against the cache rows of each token's slot, gated and projected."""
         if min(n for _, n, _, _ in plan.seqs) >= self.expand_from:
-            o = self._chunked(q, st["cache"], plan) if self.mask_kind == "chunk" and self.window > 0 else self._banded(q, st["cache"], plan)
+            o = self._chunked(q, cache, plan) if self.mask_kind == "chunk" and self.window > 0 else self._banded(q, cache, plan)
             o = H.head_gate(o, g) if g.size(1) == self.H else H.headmajor_gate(o, g)
         else:
-            o = H.window_attn(q, g, st["cache"], plan, self.H, self.G, self.D, self.V, self.scale, self.window,
-                              mask=self.mask_kind, sink=self.sink)
+            o = H.window_attn(q, g, cache, plan, self.H, self.G, self.D, self.V, self.scale, self.window,
+                              mask=self.mask_kind, sink=self.sink, cap=self.softcap, sink_vals=self.sink32)
         return H.linear(o, self.o)
 
     def _band(self, out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, slot: int, r0: int, p0: int, a: int, b: int,
@@ -393,11 +445,12 @@ class WindowAttention(nn.Module, _Fused):
         s = H.matmul_f32(qh, kt).contiguous()
         if self.p32 and q.dtype != torch.float32:  # weights as two 16-bit halves: the sum stays on the tensor cores
             pr = H.causal_softmax(s.view(Hh, nb, keys), p0 + a, self.scale, q.dtype, window=window, key0=key0, sink=self.sink,
-                                  split=True)
+                                  split=True, cap=self.softcap, sink_vals=self.sink32)
             out[:, r0 + a:r0 + b] = H.matmul_f32(pr.view(G, rep * nb, 2 * keys), torch.cat((vv, vv), 1)).view(Hh, nb, V)
             return
         pdt = torch.float32 if self.p32 else q.dtype
-        pr = H.causal_softmax(s.view(Hh, nb, keys), p0 + a, self.scale, pdt, window=window, key0=key0, sink=self.sink)
+        pr = H.causal_softmax(s.view(Hh, nb, keys), p0 + a, self.scale, pdt, window=window, key0=key0, sink=self.sink,
+                              cap=self.softcap, sink_vals=self.sink32)
         out[:, r0 + a:r0 + b] = torch.bmm(pr.view(G, rep * nb, keys), vv.to(pdt)).view(Hh, nb, V)
 
     def _banded(self, q: torch.Tensor, cache: torch.Tensor, plan: H.BatchPlan) -> torch.Tensor:
@@ -436,10 +489,12 @@ class WindowAttention(nn.Module, _Fused):
                 qh = q[r0 + a:r0 + a + nc * W].reshape(nc, W, G, rep, D).permute(0, 2, 3, 1, 4).reshape(nc * G, rep * W, D)
                 s = H.matmul_f32(qh, kt).contiguous()
                 if split:
-                    pr = H.causal_softmax(s.view(nc * Hh, W, W), 0, self.scale, q.dtype, sink=self.sink, split=True)
+                    pr = H.causal_softmax(s.view(nc * Hh, W, W), 0, self.scale, q.dtype, sink=self.sink, split=True,
+                                          cap=self.softcap, sink_vals=self.sink32)
                     o = H.matmul_f32(pr.view(nc * G, rep * W, 2 * W), torch.cat((vv, vv), 1))
                 else:
-                    pr = H.causal_softmax(s.view(nc * Hh, W, W), 0, self.scale, pdt, sink=self.sink)
+                    pr = H.causal_softmax(s.view(nc * Hh, W, W), 0, self.scale, pdt, sink=self.sink, cap=self.softcap,
+                                          sink_vals=self.sink32)
                     o = torch.bmm(pr.view(nc * G, rep * W, W), vv.to(pdt))  # [nc*G, rep*W, V]
                 out[:, r0 + a:r0 + a + nc * W] = o.view(nc, G, rep, W, V).permute(1, 2, 0, 3, 4).reshape(Hh, nc * W, V)
             tail = head + full * W
@@ -449,21 +504,39 @@ class WindowAttention(nn.Module, _Fused):
 
 
 class GatedFF(nn.Module, _Fused):
-    """``down (act(gate h) * (up h))`` without biases; gate and up are one matrix product."""
+    """``down (act(gate h) * (up h))`` without biases; gate and up are one matrix product.  ``act="clamped"`` is the
+    clamped product of :func:`mdi_llm_b200.ops.hybrid.glu` with ``limit``.  ``token_gate``: a projection ``sg [1, width]``
+    gives one logit per token whose sigmoid weighs the output; it rides in the same matrix product as gate and up (its
+    row, padded with zero rows to a multiple of 8 so the rows stay 16-byte aligned) and :meth:`gated` returns it."""
 
-    tensor_names = {"gate": "gate", "up": "up", "down": "down"}
-
-    def __init__(self, width: int, ff: int, act: str = "silu") -> None:
+    def __init__(self, width: int, ff: int, act: str = "silu", limit: float = 0.0, token_gate: bool = False) -> None:
         super().__init__()
-        self.act = act
+        self.act, self.limit, self.ff = act, float(limit), int(ff)
         self.gate, self.up, self.down = _param(ff, width), _param(ff, width), _param(width, ff)
+        self.tensor_names = {"gate": "gate", "up": "up", "down": "down"}
+        self.sg = None
+        if token_gate:
+            self.sg = _param(1, width)
+            self.tensor_names["sg"] = "sg"
 
     def finalize(self) -> None:
-        self.fuse(("gate", "up"))
+        if self.sg is None:
+            self.fuse(("gate", "up"))
+            return
+        self._pad = nn.Parameter(torch.zeros((-(2 * self.ff + 1)) % 8, self.sg.size(1), device=self.sg.device, dtype=self.sg.dtype),
+                                 requires_grad=False)
+        self.fuse(("gate", "up", "sg", "_pad"))
 
     def forward(self, h: torch.Tensor, gu: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``gu``: the gate and up projections of ``h`` side by side when the caller has already computed them."""
-        return H.linear(H.act_mul(H.linear(h, self.w_in) if gu is None else gu, self.act), self.down)
+        return H.linear(H.act_mul(H.linear(h, self.w_in) if gu is None else gu, self.act, self.limit), self.down)
+
+    def gated(self, h: torch.Tensor) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        """(output before the token gate, the gate's logit per token ``[N, 1]`` or None)."""
+        p = H.linear(h, self.w_in)
+        if self.sg is None:
+            return self.forward(h, p), None
+        return self.forward(h, p[:, :2 * self.ff]), self.col(p, "sg")
 
 
 class MoEFF(nn.Module):
@@ -474,6 +547,10 @@ class MoEFF(nn.Module):
     * ``expert="gated_silu"``, ``router="softmax"``: ``sum_e s_e down_e (silu(gate_e h) * (up_e h))`` with ``s`` the
       softmax restricted to the selected logits — the score weighs the expert's *output*.
 
+    * ``expert="clamped"``, ``router="softmax_all"``: scores are the softmax over all router outputs, the choice goes by
+      score + ``correction``, the weights are the chosen scores over their sum; experts are the clamped gated product
+      with ``limit``; the last ``identity`` router outputs have no tensors and return ``h`` itself.
+
     ``shared`` (a :class:`GatedFF`, optional) is an expert every token uses; the block adds its output.  The expert
     weights are stacked at load (``up [E, ff, C]``, or ``[E, 2 ff, C]`` with an expert's gate rows before its up rows;
     ``down [E, C, ff]``); the per-expert parameters the checkpoint names become views.  Few tokens (decoding) run two
@@ -483,19 +560,24 @@ class MoEFF(nn.Module):
     gemv_max = 64  # token-expert pairs up to which the index-driven kernels are used
 
     def __init__(self, width: int, ff: int, experts: int, top: int, router: str = "sigmoid", router_bias: bool = False,
-                 expert: str = "relu2", shared_ff: int = 0) -> None:
+                 expert: str = "relu2", shared_ff: int = 0, identity: int = 0, limit: float = 0.0, shared_limit: float = 0.0,
+                 shared_gate: bool = False) -> None:
         super().__init__()
-        self.E, self.top, self.ff = int(experts), int(top), int(ff)
-        self.mode, self.gated = router, expert == "gated_silu"
-        self.router = _param(self.E, width)
-        self.router_b = _param(self.E) if router_bias else None
+        self.E, self.top, self.ff, self.identity = int(experts), int(top), int(ff), int(identity)
+        self.mode, self.gated = router, expert in ("gated_silu", "clamped")
+        self.act, self.limit = ("clamped" if expert == "clamped" else "silu"), float(limit)
+        self.router = _param(self.E + self.identity, width)
+        self.router_b = _param(self.E + self.identity) if router_bias else None
+        self.correction = _param(self.E + self.identity) if router == "softmax_all" else None
         self.e_up = nn.ParameterList([_param(ff, width) for _ in range(self.E)])
         self.e_down = nn.ParameterList([_param(width, ff) for _ in range(self.E)])
         self.e_gate = nn.ParameterList([_param(ff, width) for _ in range(self.E)]) if self.gated else None
-        self.shared = GatedFF(width, int(shared_ff)) if shared_ff else None
+        self.shared = GatedFF(width, int(shared_ff), self.act, shared_limit, shared_gate) if shared_ff else None
 
     def names(self) -> Dict[str, nn.Parameter]:
         out = {"router": self.router}
+        if self.correction is not None:
+            out["correction"] = self.correction
         if self.router_b is not None:
             out["router.b"] = self.router_b
         for j in range(self.E):
@@ -522,25 +604,29 @@ class MoEFF(nn.Module):
                 self.e_up[j].data = self.up[j]
         self.router32 = self.router.data.float().contiguous()
         self.router_b32 = None if self.router_b is None else self.router_b.data.float().contiguous()
+        self.correction32 = None if self.correction is None else self.correction.data.float().contiguous()
         self.expert_ids = torch.arange(self.E, device=self.router.device)
         if self.shared is not None:
             self.shared.finalize()
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         N, top = h.size(0), self.top
-        idx, wt = H.router_topk(H.linear_f32(h, self.router32, self.router_b32), top, self.mode)
+        idx, wt = H.router_topk(H.linear_f32(h, self.router32, self.router_b32), top, self.mode, self.correction32)
         capturing = h.is_cuda and torch.cuda.is_current_stream_capturing()
         if N * top <= self.gemv_max or capturing:
-            return H.moe_gemv(h, idx, wt, self.up, self.down, self.gated)
+            return H.moe_gemv(h, idx, wt, self.up, self.down, self.gated, self.act, self.limit)
         flat = idx.view(-1).long()
         order = torch.argsort(flat, stable=True)
         counts = (flat[:, None] == self.expert_ids[None, :]).sum(0)  # stays on the device
         rows = (order // top).to(torch.int32)
         where = torch.empty_like(order)
         where[order] = torch.arange(order.numel(), device=order.device)
-        if self.gated:
-            mid = H.act_mul(H.grouped_linear(H.gather_scale_rows(h, rows), self.up, counts))
-            return H.combine_rows(H.grouped_linear(mid, self.down, counts), where.to(torch.int32), N, top, wt)
+        if self.gated:  # rows of identity experts sort behind the last group: no product touches them
+            mid = H.act_mul(H.grouped_linear(H.gather_scale_rows(h, rows), self.up, counts), self.act, self.limit)
+            ident = (idx, self.E, h) if self.identity else ()
+            return H.combine_rows(H.grouped_linear(mid, self.down, counts), where.to(torch.int32), N, top, wt, *ident)
+        if self.identity:
+            raise NotImplementedError("identity experts are implemented for gated experts")
         xin = H.gather_scale_rows(h, rows, wt.view(-1)[order].contiguous())
         y = H.grouped_linear(H.relu2_(H.grouped_linear(xin, self.up, counts)), self.down, counts)
         return H.combine_rows(y, where.to(torch.int32), N, top)
@@ -549,12 +635,14 @@ class MoEFF(nn.Module):
 class DenseFF(nn.Module):
     tensor_names = {"up": "up", "down": "down"}
 
-    def __init__(self, width: int, ff: int) -> None:
+    def __init__(self, width: int, ff: int, act: str = "gelu") -> None:
         super().__init__()
+        self.act = act
         self.up, self.down = _param(ff, width), _param(width, ff)
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
-        return H.linear(H.gelu_(H.linear(h, self.up)), self.down)
+        a = H.linear(h, self.up)
+        return H.linear(H.relu2_(a) if self.act == "relu2" else H.gelu_(a), self.down)
 
 
 class _LN(nn.Module):
@@ -635,6 +723,77 @@ class PreNormBlock(nn.Module):
             H.norm_accumulate(x, self.mlp(h), None, None, self.eps, "none", self.mult)
         if self.side is not None:
             self.side(x, tokens, side_table, self.eps, self.mult, dtype)
+
+
+class LightningAttention(nn.Module, _Fused):
+    """Linear attention with one fixed decay per head: ``q, k, v = silu(W h)``, ``S_t = decay_h S_(t-1) + k_t v_t^T``
+    (fp32, one ``[dim, vdim]`` matrix per head and slot, zero for a fresh slot), ``o_t = S_t^T q_t`` without a scale; the
+    heads' read-outs, side by side, get ONE RMS norm with the weight ``norm [heads * vdim]``, are multiplied by
+    ``sigmoid(W_g h)`` and projected by ``W_o``.  q, k, v and the gate are one matrix product; the SiLU of q, k, v is one
+    pass over their columns."""
+
+    tensor_names = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "norm": "norm"}
+
+    def __init__(self, width: int, m: Dict[str, Any], eps: float) -> None:
+        super().__init__()
+        self.H, self.D, self.V, self.eps = int(m["heads"]), int(m["dim"]), int(m["vdim"]), eps
+        self.decay_values = [float(x) for x in m["decay"]]
+        Hh, D, V = self.H, self.D, self.V
+        self.q, self.k, self.v, self.g = _param(Hh * D, width), _param(Hh * D, width), _param(Hh * V, width), _param(Hh * V, width)
+        self.o, self.norm = _param(width, Hh * V), _param(Hh * V)
+
+    def finalize(self) -> None:
+        self.fuse(("q", "k", "v", "g"))
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=self.q.device)
+
+    def forward(self, h: torch.Tensor, plan: H.BatchPlan, st: Dict[str, torch.Tensor]) -> torch.Tensor:
+        HD, HV = self.H * self.D, self.H * self.V
+        p = H.linear(h, self.w_in)
+        a = H.silu_rows(p[:, :2 * HD + HV])
+        o = H.lightning_recurrence(a[:, :HD], a[:, HD:2 * HD], a[:, 2 * HD:], self.decay, st["state"], plan, self.H, self.D, self.V)
+        return H.linear(H.norm_gate_rows(o, self.norm, self.col(p, "g"), self.eps, h.dtype), self.o)
+
+
+class PostNormBlock(nn.Module):
+    """``x += norm1(mixer(x))``, then ``x += norm2(ff(x))`` when the layer has a feed-forward: the sublayers read the
+    residual stream itself (rounded to the activation type), only their outputs are normed.  A mixture of experts with
+    a shared expert adds ``sigmoid(sg) * shared(x)`` to the routed sum inside the same norm."""
+
+    side = None
+
+    def __init__(self, width: int, mixer: nn.Module, ff: Optional[nn.Module], eps: float, norm: str) -> None:
+        super().__init__()
+        self.mix, self.mlp, self.eps, self.kind = mixer, ff, eps, norm
+        if norm != "rms":
+            raise ValueError("post-norm blocks are implemented with RMS norms")
+        self.norm1 = _RMS(width)
+        if ff is not None:
+            self.norm2 = _RMS(width)
+
+    def norm_names(self) -> List[str]:
+        return ["norm1"] + (["norm2"] if self.mlp is not None else [])
+
+    @staticmethod
+    def _read(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+        if dtype == torch.float32:
+            return x
+        h = torch.empty(x.shape, device=x.device, dtype=dtype)
+        H.cast_into(x, h)
+        return h
+
+    def forward(self, x: torch.Tensor, plan: H.BatchPlan, st: Dict[str, torch.Tensor], dtype: torch.dtype,
+                tokens: Optional[torch.Tensor] = None, side_table: Optional[torch.Tensor] = None) -> None:
+        H.norm_accumulate(x, self.mix(self._read(x, dtype), plan, st), self.norm1.w, None, self.eps, self.kind)
+        if self.mlp is None:
+            return
+        h = self._read(x, dtype)
+        y = self.mlp(h)
+        shared = getattr(self.mlp, "shared", None)
+        if shared is None:
+            H.norm_accumulate(x, y, self.norm2.w, None, self.eps, self.kind)
+            return
+        y2, sg = shared.gated(h)
+        H.gated_sum_norm_accumulate(x, y, y2, sg, self.norm2.w, self.eps, self.kind)
 
 
 class ParallelBlock(nn.Module):
@@ -720,6 +879,8 @@ class HybridLM(nn.Module):
                 mixer: nn.Module = LatentAttention(C, m, eps)
             elif kind == "attention":
                 mixer = WindowAttention(C, m, eps, config.attention)
+            elif kind == "lightning":
+                mixer = LightningAttention(C, m, eps)
             elif kind == "gla":
                 mixer = GatedLinearAttention(C, m, eps, ranks.get(f"l{i}.mix.a1", 16))
             else:
@@ -728,14 +889,19 @@ class HybridLM(nn.Module):
             if not mlp:
                 ff: Optional[nn.Module] = None
             elif mlp["kind"] == "moe":
+                sh = mlp.get("shared") or {}
                 ff = MoEFF(C, mlp["expert"]["ff"], mlp["router"]["experts"], mlp["router"]["top"], config.moe["router"],
-                           config.moe["router_bias"], config.moe["expert"], int((mlp.get("shared") or {}).get("ff", 0)))
+                           config.moe["router_bias"], config.moe["expert"], int(sh.get("ff", 0)),
+                           int(mlp["router"].get("identity", 0) or 0), float(mlp["expert"].get("limit", 0.0)),
+                           float(sh.get("limit", 0.0)), bool(config.moe["shared_gate"]))
             else:
-                ff = DenseFF(C, mlp["ff"])
+                ff = DenseFF(C, mlp["ff"], config.dense_act)
             if config.block == "sandwich":
                 blocks.append(SandwichBlock(C, mixer, ff, eps))
             elif config.block == "parallel":
                 blocks.append(ParallelBlock(C, mixer, ff, eps, config.norm, config.norm_offset, config.layer_scale))
+            elif config.block == "postnorm":
+                blocks.append(PostNormBlock(C, mixer, ff, eps, config.norm))
             else:
                 sd = int(config.token_side["dim"]) if config.token_side else 0
                 side = TokenSide(C, sd, i * sd) if sd else None
@@ -814,6 +980,8 @@ class HybridLM(nn.Module):
                 t = 1.0 + torch.randn(p.shape, generator=gen) * 0.1
             elif name.endswith(".vmix"):
                 t = torch.rand(p.shape, generator=gen) * 0.5 + 0.25
+            elif name.endswith(".correction"):
+                t = torch.randn(p.shape, generator=gen) * 0.05
             else:
                 t = torch.randn(p.shape, generator=gen) * 0.5
             if name == "embed":
@@ -849,7 +1017,7 @@ class HybridLM(nn.Module):
             if self.pos is not None and p0 + n > self.pos.size(0):
                 raise ValueError(f"sequence of {p0 + n} tokens exceeds the model's {self.pos.size(0)} learned positions")
         plan.shared.clear()
-        x0 = H.embed_rows(self.embed, tokens, self.pos, plan)
+        x0 = H.embed_rows(self.embed, tokens, self.pos, plan, self.config.embed_scale)
         x = x0.clone() if self.loop_in is not None else x0
         for run, (li, first) in enumerate(self.runs):
             if first:

@@ -267,6 +267,7 @@ architectures: Dict[str, Tuple[str, str]] = {
     "Badapel": ("mdi_llm_b200.models.config:HybridConfig", "mdi_llm_b200.models.hybrid:HybridLM"),
     "Vudelix": ("mdi_llm_b200.models.config:HybridConfig", "mdi_llm_b200.models.hybrid:HybridLM"),
     "Labepel": ("mdi_llm_b200.models.config:HybridConfig", "mdi_llm_b200.models.hybrid:HybridLM"),
+    "Zudovik": ("mdi_llm_b200.models.config:HybridConfig", "mdi_llm_b200.models.hybrid:HybridLM"),
 }
 
 

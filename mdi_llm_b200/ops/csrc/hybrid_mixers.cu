@@ -82,21 +82,21 @@ __device__ __forceinline__ float gelu_erff_(float x) { return 0.5f * x * (1.f + 
 // ---------------------------------------------------------------------------------------------------------
 // rows: embedding gather, casts, norms, element-wise epilogues
 // ---------------------------------------------------------------------------------------------------------
-// x[t] = table[tokens[t]] (+ pos_table[position of t] when the model has learned positions), in fp32.
+// x[t] = scale * table[tokens[t]] (+ pos_table[position of t] when the model has learned positions), in fp32.
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ x,
                                   int C, const T* __restrict__ pos_table, const int* __restrict__ meta,
-                                  const int* __restrict__ tok_seq) {
+                                  const int* __restrict__ tok_seq, float scale) {
   int t = blockIdx.x;
   const T* src = table + (size_t)tokens[t] * C;
   float* dst = x + (size_t)t * C;
   if (pos_table) {
     const int* m = meta + 4 * tok_seq[t];
     const T* pr = pos_table + (size_t)(m[3] + (t - m[0])) * C;
-    for (int i = threadIdx.x; i < C; i += blockDim.x) dst[i] = to_f(src[i]) + to_f(pr[i]);
+    for (int i = threadIdx.x; i < C; i += blockDim.x) dst[i] = scale * to_f(src[i]) + to_f(pr[i]);
     return;
   }
-  for (int i = threadIdx.x; i < C; i += blockDim.x) dst[i] = to_f(src[i]);
+  for (int i = threadIdx.x; i < C; i += blockDim.x) dst[i] = scale * to_f(src[i]);
 }
 
 template <typename Tin, typename Tout>
@@ -355,13 +355,22 @@ __global__ void latent_combine_kernel(const float* __restrict__ part_acc, const 
 // sink != 0: one more slot of score zero joins the denominator (it has no value): p_j = e^{s_j} / (1 + sum e^{s_k}).
 // split != 0: a row of p is 2 * keys wide: the weights rounded to T, and behind them the remainders (weight minus its
 // rounding) rounded to T, so that a matrix product with the values stacked twice sums the weights to 16 mantissa bits.
+// cap > 0: the scaled score becomes cap * tanh(scaled score / cap) before the softmax (the transform is applied where a
+// score is read; from there on the scale is 1).  sink_vals (with sink != 0): the sink's score is sink_vals[head]
+// instead of zero, head = (row / rows_per_head) % sink_heads; it is neither scaled nor capped.
 #define CS_CACHE 8  // scores a thread keeps in registers: rows of up to 8 * 256 keys are read once
 template <typename T>
 __global__ void causal_softmax_kernel(const float* __restrict__ s, T* __restrict__ p, int rows_per_head, int keys,
-                                      int first_pos, float scale, int window, int key0, int sink, int split) {
+                                      int first_pos, float scale, int window, int key0, int sink, int split,
+                                      float cap, const float* __restrict__ sink_vals, int sink_heads) {
   __shared__ float red[33];
   size_t row = blockIdx.x;
   int i = (int)(row % rows_per_head);
+  const float raw_scale = scale, inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+  if (cap > 0.f) scale = 1.f;
+#define CS_SCORE(x) (cap > 0.f ? cap * tanhf((x) * raw_scale * inv_cap) : (x))
+  // the sink's score in the units of the stored scores (they are multiplied by `scale` inside the exponent)
+  const float sink_raw = sink && sink_vals ? sink_vals[(row / rows_per_head) % sink_heads] / scale : 0.f;
   int pos = first_pos + i;  // column j is position key0 + j; visible: pos - window < key0 + j <= pos
   int vis = max(0, min(keys, pos - key0 + 1));
   int lo = window > 0 ? max(0, pos - window + 1 - key0) : 0;
@@ -379,7 +388,7 @@ __global__ void causal_softmax_kernel(const float* __restrict__ s, T* __restrict
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
       int j = j0 + c;
-      if (!(mine && j >= lo && j < vis)) v[c] = -INFINITY;
+      v[c] = mine && j >= lo && j < vis ? CS_SCORE(v[c]) : -INFINITY;
       m = fmaxf(m, v[c]);
     }
     m = warp_max(m);
@@ -387,7 +396,7 @@ __global__ void causal_softmax_kernel(const float* __restrict__ s, T* __restrict
     __syncthreads();
     m = -INFINITY;
     for (int w = 0; w < (blockDim.x + 31) / 32; ++w) m = fmaxf(m, red[w]);
-    if (sink) m = fmaxf(m, 0.f);
+    if (sink) m = fmaxf(m, sink_raw);
     float sum = 0.f;
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
@@ -395,7 +404,7 @@ __global__ void causal_softmax_kernel(const float* __restrict__ s, T* __restrict
       sum += v[c];
     }
     sum = block_sum(sum, red);
-    if (sink) sum += expf(-m * scale);
+    if (sink) sum += expf((sink_raw - m) * scale);
     float inv = 1.f / sum;
     if (!mine) return;
     float rest[8];
@@ -412,11 +421,11 @@ __global__ void causal_softmax_kernel(const float* __restrict__ s, T* __restrict
 #pragma unroll
     for (int c = 0; c < CS_CACHE; ++c) {
       int j = threadIdx.x + c * blockDim.x;
-      v[c] = j >= lo && j < vis ? src[j] : -INFINITY;
+      v[c] = j >= lo && j < vis ? CS_SCORE(src[j]) : -INFINITY;
       m = fmaxf(m, v[c]);
     }
   } else {
-    for (int j = lo + threadIdx.x; j < vis; j += blockDim.x) m = fmaxf(m, src[j]);
+    for (int j = lo + threadIdx.x; j < vis; j += blockDim.x) m = fmaxf(m, CS_SCORE(src[j]));
   }
   m = warp_max(m);
   __syncthreads();
@@ -424,7 +433,7 @@ __global__ void causal_softmax_kernel(const float* __restrict__ s, T* __restrict
   __syncthreads();
   m = -INFINITY;
   for (int w = 0; w < (blockDim.x + 31) / 32; ++w) m = fmaxf(m, red[w]);
-  if (sink) m = fmaxf(m, 0.f);  // scale > 0: the shift that keeps every exponent <= 0
+  if (sink) m = fmaxf(m, sink_raw);  // scale > 0: the shift that keeps every exponent <= 0
   float sum = 0.f;
   if (cached) {
 #pragma unroll
@@ -433,10 +442,10 @@ __global__ void causal_softmax_kernel(const float* __restrict__ s, T* __restrict
       sum += v[c];
     }
   } else {
-    for (int j = lo + threadIdx.x; j < vis; j += blockDim.x) sum += expf((src[j] - m) * scale);
+    for (int j = lo + threadIdx.x; j < vis; j += blockDim.x) sum += expf((CS_SCORE(src[j]) - m) * scale);
   }
   sum = block_sum(sum, red);
-  if (sink) sum += expf(-m * scale);
+  if (sink) sum += expf((sink_raw - m) * scale);
   float inv = 1.f / sum;
   if (cached) {
 #pragma unroll
@@ -452,11 +461,12 @@ __global__ void causal_softmax_kernel(const float* __restrict__ s, T* __restrict
     return;
   }
   for (int j = threadIdx.x; j < keys; j += blockDim.x) {
-    float w = j >= lo && j < vis ? expf((src[j] - m) * scale) * inv : 0.f;
+    float w = j >= lo && j < vis ? expf((CS_SCORE(src[j]) - m) * scale) * inv : 0.f;
     T hi = from_f<T>(w);
     dst[j] = hi;
     if (split) dst[keys + j] = from_f<T>(w - to_f(hi));
   }
+#undef CS_SCORE
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -832,14 +842,14 @@ extern "C" {
 
 // dtype codes: 0 = bf16, 1 = fp32
 int hyb_embed_rows(const void* table, const int* tokens, float* x, int N, int C, const void* pos_table,
-                   const int* meta, const int* tok_seq, int dt, cudaStream_t st) {
+                   const int* meta, const int* tok_seq, float scale, int dt, cudaStream_t st) {
   if (N == 0) return 0;
   if (pos_table && (!meta || !tok_seq)) return -2;
   HYB_DISPATCH(dt,
                (embed_rows_kernel<bf16><<<N, 256, 0, st>>>((const bf16*)table, tokens, x, C, (const bf16*)pos_table, meta,
-                                                           tok_seq)),
+                                                           tok_seq, scale)),
                (embed_rows_kernel<float><<<N, 256, 0, st>>>((const float*)table, tokens, x, C, (const float*)pos_table,
-                                                            meta, tok_seq)));
+                                                            meta, tok_seq, scale)));
   return (int)cudaGetLastError();
 }
 
@@ -948,15 +958,17 @@ int hyb_latent_attn(const void* qlat, const void* q, long long q_stride, const v
 }
 
 int hyb_causal_softmax(const float* s, void* p, long long rows, int rows_per_head, int keys, int first_pos, float scale,
-                       int window, int key0, int sink, int split, int dt, cudaStream_t st) {
+                       int window, int key0, int sink, int split, float cap, const float* sink_vals, int sink_heads,
+                       int dt, cudaStream_t st) {
   if (rows == 0) return 0;
   if (scale <= 0.f) return -3;  // the row maximum is taken before scaling
+  if (sink_vals && sink_heads < 1) return -2;
   // rows of up to 2048 keys in multiples of 8: 8 keys per thread, so only as many warps as the row needs
   int th = (keys & 7) == 0 && keys <= 2048 ? ((keys / 8 + 31) / 32) * 32 : 256;
   if (th != 256 || ((keys & 7) == 0 && keys <= 2048))
     if (((uintptr_t)s | (uintptr_t)p) & 15) return -4;  // the 16-byte loads and stores of that form
-  HYB_DISPATCH(dt, (causal_softmax_kernel<bf16><<<(unsigned)rows, th, 0, st>>>(s, (bf16*)p, rows_per_head, keys, first_pos, scale, window, key0, sink, split)),
-               (causal_softmax_kernel<float><<<(unsigned)rows, th, 0, st>>>(s, (float*)p, rows_per_head, keys, first_pos, scale, window, key0, sink, split)));
+  HYB_DISPATCH(dt, (causal_softmax_kernel<bf16><<<(unsigned)rows, th, 0, st>>>(s, (bf16*)p, rows_per_head, keys, first_pos, scale, window, key0, sink, split, cap, sink_vals, sink_heads)),
+               (causal_softmax_kernel<float><<<(unsigned)rows, th, 0, st>>>(s, (float*)p, rows_per_head, keys, first_pos, scale, window, key0, sink, split, cap, sink_vals, sink_heads)));
   return (int)cudaGetLastError();
 }
 
@@ -1140,6 +1152,8 @@ __global__ void window_append_kernel(T* __restrict__ q, long long q_stride, cons
 // mask_kind 0: the last `window` positions (0 = all earlier ones); 1: the positions of the token's own block of `window`
 // positions, blocks numbered from the first position of the sequence.  sink != 0: a slot of score zero without a value joins the
 // softmax denominator.  gate_mode 1: sigmoid(gate[t, h]) per head; 2: sigmoid(gate[t, h * V + d]) per output channel.
+// cap > 0: a scaled score s becomes cap * tanh(s / cap).  sink_vals (with sink != 0): the sink's score is sink_vals[h]
+// (fp32, neither scaled nor capped) instead of zero.
 #define WT_TILE 32
 #define WT_MAXV 8
 template <typename T>
@@ -1148,7 +1162,7 @@ __global__ void window_attn_kernel(const T* __restrict__ q, long long q_stride, 
                                    const int* __restrict__ meta, const int* __restrict__ tok_seq, T* __restrict__ out,
                                    int H, int G, int D, int V, float scale, int window, int nsplit,
                                    float* __restrict__ part_acc, float* __restrict__ part_ml, int mask_kind, int sink,
-                                   int gate_mode, int vec) {
+                                   int gate_mode, int vec, float cap, const float* __restrict__ sink_vals) {
   extern __shared__ float sm[];
   int rep = H / G;
   float* qs = sm;                       // [rep][D]
@@ -1223,6 +1237,7 @@ __global__ void window_attn_kernel(const T* __restrict__ q, long long q_stride, 
       float a = 0.f;
       for (int d = 0; d < D; ++d) a += qr[d] * kr[d];
       s = a * scale;
+      if (cap > 0.f) s = cap * tanhf(s / cap);
     }
     float mn = fmaxf(mx, warp_max(s));
     float pj = j0 + lane <= pos ? expf(s - mn) : 0.f;
@@ -1251,9 +1266,10 @@ __global__ void window_attn_kernel(const T* __restrict__ q, long long q_stride, 
     if (lane == 0) { part_ml[2 * row] = mx; part_ml[2 * row + 1] = l; }
     return;
   }
-  if (sink) {  // the zero-score slot: shift to max(mx, 0), add its weight to the denominator
-    float mn = fmaxf(mx, 0.f), corr = expf(mx - mn);
-    l = l * corr + expf(-mn);
+  if (sink) {  // the slot without a value: shift to max(mx, its score), add its weight to the denominator
+    float sv = sink_vals ? sink_vals[h] : 0.f;
+    float mn = fmaxf(mx, sv), corr = expf(mx - mn);
+    l = l * corr + expf(sv - mn);
 #pragma unroll
     for (int c = 0; c < WT_MAXV; ++c) acc[c] *= corr;
   }
@@ -1276,7 +1292,7 @@ __global__ void window_attn_kernel(const T* __restrict__ q, long long q_stride, 
 template <typename T>
 __global__ void window_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                       const T* __restrict__ gate, long long g_stride, T* __restrict__ out, int N, int H,
-                                      int V, int nsplit, int sink, int gate_mode) {
+                                      int V, int nsplit, int sink, int gate_mode, const float* __restrict__ sink_vals) {
   int t = blockIdx.x, h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (h >= H) return;
   float ms = -INFINITY, ls = 0.f;
@@ -1286,9 +1302,10 @@ __global__ void window_combine_kernel(const float* __restrict__ part_acc, const 
     ls = ml[1];
   }
   float M = warp_max(ms);
-  if (sink) M = fmaxf(M, 0.f);
+  float sv = sink && sink_vals ? sink_vals[h] : 0.f;
+  if (sink) M = fmaxf(M, sv);
   float ws = lane < nsplit ? expf(ms - M) : 0.f;  // a share without keys: exp(-inf) = 0
-  float l = warp_sum(ls * ws) + (sink ? expf(-M) : 0.f);
+  float l = warp_sum(ls * ws) + (sink ? expf(sv - M) : 0.f);
   float gt = gate && gate_mode == 1 ? sigmoidf_(to_f(gate[(size_t)t * g_stride + h])) : 1.f;
   if ((V & 3) == 0) {  // four channels per lane, eight shares' loads in flight: the merge is a chain of round trips
     for (int d0 = 0; d0 < V; d0 += 128) {
@@ -1355,12 +1372,37 @@ __global__ void token_side_gate_kernel(const T* __restrict__ z, long long z_stri
 }
 
 // One thread per token: the `top` largest logits (ties to the lower index).  mode 0: scores = sigmoid(logit), each
-// on its own; mode 1: scores = softmax restricted to the selected logits.
+// on its own; mode 1: scores = softmax restricted to the selected logits; mode 2: scores s = softmax over ALL E logits,
+// the choice goes by s + correction (correction: E floats, optional), the weights are the chosen s divided by their
+// sum + 1e-20.
 __global__ void router_topk_kernel(const float* __restrict__ z, int* __restrict__ idx, float* __restrict__ wt, int N,
-                                   int E, int top, int mode) {
+                                   int E, int top, int mode, const float* __restrict__ correction) {
   int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= N) return;
   const float* row = z + (size_t)t * E;
+  if (mode == 2) {
+    float m = -INFINITY, den = 0.f;
+    for (int e = 0; e < E; ++e) m = fmaxf(m, row[e]);
+    for (int e = 0; e < E; ++e) den += expf(row[e] - m);
+    float tot = 0.f;
+    for (int k = 0; k < top; ++k) {
+      int best = -1;
+      float bv = -INFINITY, bs = 0.f;
+      for (int e = 0; e < E; ++e) {
+        bool taken = false;
+        for (int j = 0; j < k; ++j) taken |= idx[(size_t)t * top + j] == e;
+        float sc = expf(row[e] - m) / den;
+        float v = correction ? sc + correction[e] : sc;
+        if (!taken && (best < 0 || v > bv)) { best = e; bv = v; bs = sc; }
+      }
+      idx[(size_t)t * top + k] = best;
+      wt[(size_t)t * top + k] = bs;
+      tot += bs;
+    }
+    tot += 1e-20f;
+    for (int k = 0; k < top; ++k) wt[(size_t)t * top + k] /= tot;
+    return;
+  }
   for (int k = 0; k < top; ++k) {
     int best = -1;
     float bv = -INFINITY;
@@ -1404,12 +1446,21 @@ __device__ __forceinline__ float dot_row(const T* __restrict__ wrow, const float
 //   MODE 1 (down): y[p, c] = w[e][c, :] . a[p, :]                                    a fp32, K = ff
 //   MODE 2 (gated up): y[p, f] = silu(w[e][f, :] . x) * (w[e][R + f, :] . x), x = x[p / top, :] unscaled; an expert's
 //                  matrix is [2R, K], its gate rows first and its up rows behind them
+//                  glu 0: silu(g) * u as above; glu 1 (clamped): g' = min(g, limit), u' = clamp(u, -limit, limit),
+//                  y = g' * sigmoid(1.702 g') * (u' + 1)
+// A pair whose index is not below the grid's expert count (an identity expert: no tensors) is served by no block.
 #define MOE_ROWS 32
 #define MOE_PCH 4
+__device__ __forceinline__ float glu_act(float g, float u, int glu, float limit) {
+  if (glu == 0) return siluf_(g) * u;
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g * sigmoidf_(1.702f * g) * (u + 1.f);
+}
 template <typename T, int MODE>
 __global__ void moe_pairs_kernel(const void* __restrict__ xin, long long x_stride, const int* __restrict__ idx,
                                  const float* __restrict__ wt, const T* __restrict__ w, float* __restrict__ y, int P,
-                                 int top, int K, int R, int pch) {
+                                 int top, int K, int R, int pch, int glu, float limit) {
   extern __shared__ float sm[];  // [pch][K]
   __shared__ int match[MOE_PCH];
   __shared__ int s_cnt, s_next;
@@ -1497,7 +1548,7 @@ __global__ void moe_pairs_kernel(const void* __restrict__ xin, long long x_strid
           float g = MODE == 2 ? warp_sum(first[m]) : 0.f;
           if (lane == 0) {
             if (MODE == 0) { v = fmaxf(v, 0.f); v = v * v; }
-            if (MODE == 2) v *= siluf_(g);
+            if (MODE == 2) v = glu_act(g, v, glu, limit);
             y[(size_t)match[m] * R + f] = v;
           }
         }
@@ -1527,7 +1578,7 @@ template <int MODE>
 __global__ void __launch_bounds__(256) moe_pairs_stream_kernel(const void* __restrict__ xin, long long x_stride,
                                                                const int* __restrict__ idx, const float* __restrict__ wt,
                                                                const bf16* __restrict__ w, float* __restrict__ y, int P,
-                                                               int top, int K, int R, int pch) {
+                                                               int top, int K, int R, int pch, int glu, float limit) {
   constexpr int KC = MODE == 2 ? 128 : 256;  // columns per chunk
   constexpr int LPR = KC / 8;                // lanes per row of a chunk
   extern __shared__ __align__(16) unsigned char ms_raw[];
@@ -1630,7 +1681,7 @@ __global__ void __launch_bounds__(256) moe_pairs_stream_kernel(const void* __res
 #pragma unroll
             for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
             float g = __shfl_sync(0xffffffffu, v, 0), u = __shfl_sync(0xffffffffu, v, 16);
-            v = siluf_(g) * u;
+            v = glu_act(g, u, glu, limit);
           } else {
             v = warp_sum(v);
             if (MODE == 0) { v = fmaxf(v, 0.f); v = v * v; }
@@ -1643,14 +1694,19 @@ __global__ void __launch_bounds__(256) moe_pairs_stream_kernel(const void* __res
   }
 }
 
-// out[t, c] = sum_k wt[t * top + k] * y[t * top + k, c] (wt absent: plain sum), summed in the order of k.
+// out[t, c] = sum_k wt[t * top + k] * y[t * top + k, c] (wt absent: plain sum), summed in the order of k.  With `idx`,
+// a choice whose index is E or more is an identity expert: its term is wt * h[t, c], the token's own input row.
 template <typename T>
 __global__ void moe_sum_kernel(const float* __restrict__ y, const float* __restrict__ wt, T* __restrict__ out, int top,
-                               int C) {
+                               int C, const int* __restrict__ idx, int E, const T* __restrict__ h, long long h_stride) {
   int t = blockIdx.x;
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
     float a = 0.f;
-    for (int k = 0; k < top; ++k) a += (wt ? wt[(size_t)t * top + k] : 1.f) * y[((size_t)t * top + k) * C + c];
+    for (int k = 0; k < top; ++k) {
+      size_t p = (size_t)t * top + k;
+      float term = idx && idx[p] >= E ? to_f(h[(size_t)t * h_stride + c]) : y[p * C + c];
+      a += (wt ? wt[p] : 1.f) * term;
+    }
     out[(size_t)t * C + c] = from_f<T>(a);
   }
 }
@@ -1668,36 +1724,45 @@ __global__ void gather_scale_rows_kernel(const T* __restrict__ h, long long h_st
   for (int c = threadIdx.x; c < C; c += blockDim.x) out[(size_t)i * C + c] = from_f<T>(w * to_f(src[c]));
 }
 
+// With `idx`, a choice whose index is E or more is an identity expert: its term is wt * h[t, c] and its row of y is
+// not read.
 template <typename T>
 __global__ void combine_rows_kernel(const T* __restrict__ y, const int* __restrict__ where, const float* __restrict__ wt,
-                                    T* __restrict__ out, int top, int C) {
+                                    T* __restrict__ out, int top, int C, const int* __restrict__ idx, int E,
+                                    const T* __restrict__ h, long long h_stride) {
   int t = blockIdx.x;
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
     float a = 0.f;
-    for (int k = 0; k < top; ++k)
-      a += (wt ? wt[(size_t)t * top + k] : 1.f) * to_f(y[(size_t)where[(size_t)t * top + k] * C + c]);
+    for (int k = 0; k < top; ++k) {
+      size_t p = (size_t)t * top + k;
+      float term = idx && idx[p] >= E ? to_f(h[(size_t)t * h_stride + c]) : to_f(y[(size_t)where[p] * C + c]);
+      a += (wt ? wt[p] : 1.f) * term;
+    }
     out[(size_t)t * C + c] = from_f<T>(a);
   }
 }
 
 // out[r, f] = act(in[r, f]) * in[r, F + f]: the product of a gated feed-forward whose gate and up projections are
-// the two halves of one row.  act 0: silu, 1: gelu (tanh form).
+// the two halves of one row.  act 0: silu, 1: gelu (tanh form), 2: the clamped form of glu_act with `limit`.
+__device__ __forceinline__ float act_mul_one(float g, float u, int act, float limit) {
+  return act == 2 ? glu_act(g, u, 1, limit) : (act == 0 ? siluf_(g) : gelu_tanhf_(g)) * u;
+}
 template <typename T>
 __global__ void act_mul_rows_kernel(const T* __restrict__ in, long long in_stride, T* __restrict__ out, int F, int act,
-                                    long long total) {
+                                    long long total, float limit) {
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   long long r = i / F;
   int f = (int)(i - r * F);
   const T* row = in + (size_t)r * in_stride;
   float g = to_f(row[f]), u = to_f(row[F + f]);
-  out[i] = from_f<T>((act == 0 ? siluf_(g) : gelu_tanhf_(g)) * u);
+  out[i] = from_f<T>(act_mul_one(g, u, act, limit));
 }
 
 // The same, 8 values per thread with 16-byte loads and stores (F and the row stride multiples of 8, bases aligned).
 template <typename T>
 __global__ void act_mul_rows_vec_kernel(const T* __restrict__ in, long long in_stride, T* __restrict__ out, int F, int act,
-                                        long long total8) {
+                                        long long total8, float limit) {
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total8) return;
   int f8 = F >> 3;
@@ -1708,7 +1773,7 @@ __global__ void act_mul_rows_vec_kernel(const T* __restrict__ in, long long in_s
   load8(row + c, g);
   load8(row + F + c, u);
 #pragma unroll
-  for (int e = 0; e < 8; ++e) g[e] = (act == 0 ? siluf_(g[e]) : gelu_tanhf_(g[e])) * u[e];
+  for (int e = 0; e < 8; ++e) g[e] = act_mul_one(g[e], u[e], act, limit);
   store8(out + (size_t)r * F + c, g);
 }
 
@@ -1759,7 +1824,7 @@ int hyb_window_append(void* q, long long q_stride, const void* k, long long k_st
 int hyb_window_attn(const void* q, long long q_stride, const void* gate, long long g_stride, const void* cache,
                     long long slot_stride, const int* meta, const int* tok_seq, void* out, int N, int H, int G, int D,
                     int V, float scale, int window, int nsplit, float* part_acc, float* part_ml, int mask_kind, int sink,
-                    int gate_mode, int dt, cudaStream_t st) {
+                    int gate_mode, float cap, const float* sink_vals, int dt, cudaStream_t st) {
   if (N == 0) return 0;
   if (mask_kind < 0 || mask_kind > 1 || (mask_kind == 1 && window < 1) || gate_mode < 0 || gate_mode > 2) return -3;
   int rep = G > 0 ? H / G : 0;
@@ -1777,17 +1842,17 @@ int hyb_window_attn(const void* q, long long q_stride, const void* gate, long lo
     window_attn_kernel<bf16><<<grid, 32 * rep, smem, st>>>((const bf16*)q, q_stride, (const bf16*)gate, g_stride,
                                                            (const bf16*)cache, slot_stride, meta, tok_seq, (bf16*)out, H,
                                                            G, D, V, scale, window, nsplit, part_acc, part_ml, mask_kind, sink,
-                                                           gate_mode, vec);
+                                                           gate_mode, vec, cap, sink_vals);
     if (nsplit > 1)
-      window_combine_kernel<bf16><<<cgrid, 128, 0, st>>>(part_acc, part_ml, (const bf16*)gate, g_stride, (bf16*)out, N, H, V, nsplit, sink, gate_mode);
+      window_combine_kernel<bf16><<<cgrid, 128, 0, st>>>(part_acc, part_ml, (const bf16*)gate, g_stride, (bf16*)out, N, H, V, nsplit, sink, gate_mode, sink_vals);
   } else {
     if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(window_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
     window_attn_kernel<float><<<grid, 32 * rep, smem, st>>>((const float*)q, q_stride, (const float*)gate, g_stride,
                                                             (const float*)cache, slot_stride, meta, tok_seq, (float*)out,
                                                             H, G, D, V, scale, window, nsplit, part_acc, part_ml, mask_kind, sink,
-                                                            gate_mode, vec);
+                                                            gate_mode, vec, cap, sink_vals);
     if (nsplit > 1)
-      window_combine_kernel<float><<<cgrid, 128, 0, st>>>(part_acc, part_ml, (const float*)gate, g_stride, (float*)out, N, H, V, nsplit, sink, gate_mode);
+      window_combine_kernel<float><<<cgrid, 128, 0, st>>>(part_acc, part_ml, (const float*)gate, g_stride, (float*)out, N, H, V, nsplit, sink, gate_mode, sink_vals);
   }
   return (int)cudaGetLastError();
 }
@@ -1815,10 +1880,11 @@ int hyb_token_side_gate(const void* z, long long z_stride, const void* table, lo
   return (int)cudaGetLastError();
 }
 
-int hyb_router_topk(const float* z, int* idx, float* wt, int N, int E, int top, int mode, cudaStream_t st) {
+int hyb_router_topk(const float* z, int* idx, float* wt, int N, int E, int top, int mode, const float* correction,
+                    cudaStream_t st) {
   if (N == 0) return 0;
-  if (top < 1 || top > E || mode < 0 || mode > 1) return -3;
-  router_topk_kernel<<<(N + 63) / 64, 64, 0, st>>>(z, idx, wt, N, E, top, mode);
+  if (top < 1 || top > E || mode < 0 || mode > 2) return -3;
+  router_topk_kernel<<<(N + 63) / 64, 64, 0, st>>>(z, idx, wt, N, E, top, mode, correction);
   return (int)cudaGetLastError();
 }
 
@@ -1826,7 +1892,7 @@ int hyb_router_topk(const float* z, int* idx, float* wt, int N, int E, int top, 
 
 template <typename T, int MODE>
 static int launch_moe_pairs(const void* x, long long x_stride, const int* idx, const float* wt, const void* w, float* y,
-                            int P, int top, int K, int R, int E, cudaStream_t st) {
+                            int P, int top, int K, int R, int E, cudaStream_t st, int glu = 0, float limit = 0.f) {
   // shared memory only for the pairs there can be, and at most 64 KB while more than one pair is staged: three
   // blocks per SM keep more weight loads in flight than one block that serves four pairs at once
   int pch = P < MOE_PCH ? P : MOE_PCH;
@@ -1839,7 +1905,7 @@ static int launch_moe_pairs(const void* x, long long x_stride, const int* idx, c
         cudaError_t e = cudaFuncSetAttribute(moe_pairs_stream_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ssm);
         if (e != cudaSuccess) return (int)e;
         dim3 sgrid(E, (R + MOE_ROWS - 1) / MOE_ROWS);
-        moe_pairs_stream_kernel<MODE><<<sgrid, 256, ssm, st>>>(x, x_stride, idx, wt, (const bf16*)w, y, P, top, K, R, spch);
+        moe_pairs_stream_kernel<MODE><<<sgrid, 256, ssm, st>>>(x, x_stride, idx, wt, (const bf16*)w, y, P, top, K, R, spch, glu, limit);
         return (int)cudaGetLastError();
       }
     }
@@ -1852,7 +1918,7 @@ static int launch_moe_pairs(const void* x, long long x_stride, const int* idx, c
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid(E, (R + MOE_ROWS - 1) / MOE_ROWS);
-  moe_pairs_kernel<T, MODE><<<grid, 256, smem, st>>>(x, x_stride, idx, wt, (const T*)w, y, P, top, K, R, pch);
+  moe_pairs_kernel<T, MODE><<<grid, 256, smem, st>>>(x, x_stride, idx, wt, (const T*)w, y, P, top, K, R, pch, glu, limit);
   return (int)cudaGetLastError();
 }
 
@@ -1860,12 +1926,14 @@ extern "C" {
 
 // act [N*top, ff] fp32.  gated 0: squared-ReLU of the chosen experts' up projections of the score-weighted token
 // (up [E, ff, C]).  gated 1: silu(gate x) * (up x) of the token as it is (up [E, 2 ff, C], gate rows first).
+// gated 2: the clamped form (glu_act) with `limit`.
 int hyb_moe_up(const void* h, long long h_stride, const int* idx, const float* wt, const void* up, float* act, int N,
-               int top, int C, int ff, int E, int gated, int dt, cudaStream_t st) {
+               int top, int C, int ff, int E, int gated, float limit, int dt, cudaStream_t st) {
   if (N == 0) return 0;
+  if (gated < 0 || gated > 2) return -3;
   if (gated) {
-    if (dt == 0) return launch_moe_pairs<bf16, 2>(h, h_stride, idx, wt, up, act, N * top, top, C, ff, E, st);
-    return launch_moe_pairs<float, 2>(h, h_stride, idx, wt, up, act, N * top, top, C, ff, E, st);
+    if (dt == 0) return launch_moe_pairs<bf16, 2>(h, h_stride, idx, wt, up, act, N * top, top, C, ff, E, st, gated - 1, limit);
+    return launch_moe_pairs<float, 2>(h, h_stride, idx, wt, up, act, N * top, top, C, ff, E, st, gated - 1, limit);
   }
   if (!wt) return -2;
   if (dt == 0) return launch_moe_pairs<bf16, 0>(h, h_stride, idx, wt, up, act, N * top, top, C, ff, E, st);
@@ -1873,15 +1941,16 @@ int hyb_moe_up(const void* h, long long h_stride, const int* idx, const float* w
 }
 
 // out [N, C] = sum over a token's choices of the expert's down projection of act, each times wt[choice] when wt is
-// given; ypair [N*top, C] fp32 is scratch.
+// given; ypair [N*top, C] fp32 is scratch.  With h, a choice of index >= E adds wt * h[token] (an identity expert).
 int hyb_moe_down(const float* act, const int* idx, const float* wt, const void* down, float* ypair, void* out, int N,
-                 int top, int C, int ff, int E, int dt, cudaStream_t st) {
+                 int top, int C, int ff, int E, const void* h, long long h_stride, int dt, cudaStream_t st) {
   if (N == 0) return 0;
   int rc = dt == 0 ? launch_moe_pairs<bf16, 1>(act, ff, idx, nullptr, down, ypair, N * top, top, ff, C, E, st)
                    : launch_moe_pairs<float, 1>(act, ff, idx, nullptr, down, ypair, N * top, top, ff, C, E, st);
   if (rc) return rc;
-  HYB_DISPATCH(dt, (moe_sum_kernel<bf16><<<N, 256, 0, st>>>(ypair, wt, (bf16*)out, top, C)),
-               (moe_sum_kernel<float><<<N, 256, 0, st>>>(ypair, wt, (float*)out, top, C)));
+  const int* ix = h ? idx : nullptr;
+  HYB_DISPATCH(dt, (moe_sum_kernel<bf16><<<N, 256, 0, st>>>(ypair, wt, (bf16*)out, top, C, ix, E, (const bf16*)h, h_stride)),
+               (moe_sum_kernel<float><<<N, 256, 0, st>>>(ypair, wt, (float*)out, top, C, ix, E, (const float*)h, h_stride)));
   return (int)cudaGetLastError();
 }
 
@@ -1894,29 +1963,30 @@ int hyb_gather_scale_rows(const void* h, long long h_stride, const int* rows, co
   return (int)cudaGetLastError();
 }
 
-int hyb_combine_rows(const void* y, const int* where, const float* wt, void* out, int n, int top, int C, int dt,
-                     cudaStream_t st) {
+int hyb_combine_rows(const void* y, const int* where, const float* wt, void* out, int n, int top, int C, const int* idx,
+                     int E, const void* h, long long h_stride, int dt, cudaStream_t st) {
   if (n == 0) return 0;
-  HYB_DISPATCH(dt, (combine_rows_kernel<bf16><<<n, 256, 0, st>>>((const bf16*)y, where, wt, (bf16*)out, top, C)),
-               (combine_rows_kernel<float><<<n, 256, 0, st>>>((const float*)y, where, wt, (float*)out, top, C)));
+  if (idx && !h) return -2;
+  HYB_DISPATCH(dt, (combine_rows_kernel<bf16><<<n, 256, 0, st>>>((const bf16*)y, where, wt, (bf16*)out, top, C, idx, E, (const bf16*)h, h_stride)),
+               (combine_rows_kernel<float><<<n, 256, 0, st>>>((const float*)y, where, wt, (float*)out, top, C, idx, E, (const float*)h, h_stride)));
   return (int)cudaGetLastError();
 }
 
-int hyb_act_mul_rows(const void* in, long long in_stride, void* out, long long rows, int F, int act, int dt,
+int hyb_act_mul_rows(const void* in, long long in_stride, void* out, long long rows, int F, int act, float limit, int dt,
                      cudaStream_t st) {
   long long total = rows * F;
   if (total == 0) return 0;
-  if (act < 0 || act > 1) return -3;
+  if (act < 0 || act > 2) return -3;
   if (F % 8 == 0 && in_stride % 8 == 0 && (uintptr_t)in % 32 == 0 && (uintptr_t)out % 32 == 0) {
     long long total8 = total / 8;
     unsigned vb = (unsigned)((total8 + 255) / 256);
-    HYB_DISPATCH(dt, (act_mul_rows_vec_kernel<bf16><<<vb, 256, 0, st>>>((const bf16*)in, in_stride, (bf16*)out, F, act, total8)),
-                 (act_mul_rows_vec_kernel<float><<<vb, 256, 0, st>>>((const float*)in, in_stride, (float*)out, F, act, total8)));
+    HYB_DISPATCH(dt, (act_mul_rows_vec_kernel<bf16><<<vb, 256, 0, st>>>((const bf16*)in, in_stride, (bf16*)out, F, act, total8, limit)),
+                 (act_mul_rows_vec_kernel<float><<<vb, 256, 0, st>>>((const float*)in, in_stride, (float*)out, F, act, total8, limit)));
     return (int)cudaGetLastError();
   }
   unsigned blocks = (unsigned)((total + 255) / 256);
-  HYB_DISPATCH(dt, (act_mul_rows_kernel<bf16><<<blocks, 256, 0, st>>>((const bf16*)in, in_stride, (bf16*)out, F, act, total)),
-               (act_mul_rows_kernel<float><<<blocks, 256, 0, st>>>((const float*)in, in_stride, (float*)out, F, act, total)));
+  HYB_DISPATCH(dt, (act_mul_rows_kernel<bf16><<<blocks, 256, 0, st>>>((const bf16*)in, in_stride, (bf16*)out, F, act, total, limit)),
+               (act_mul_rows_kernel<float><<<blocks, 256, 0, st>>>((const float*)in, in_stride, (float*)out, F, act, total, limit)));
   return (int)cudaGetLastError();
 }
 
@@ -1936,3 +2006,408 @@ int hyb_scaled_branches(float* x, long long x_stride, const void* a, long long a
 }
 
 }  // extern "C"
+
+// =========================================================================================================
+// post-norm blocks: norm over a whole projection before the rotation, the fixed-decay linear recurrence
+// ("lightning" attention) in a token-scan and a chunked form, and the norm of a gated sum of two branches
+// =========================================================================================================
+namespace hyb {
+
+// One block per token.  The query row (all H heads, H * D values) is divided by ITS root mean square over all H * D
+// values (eps inside the root) and multiplied by qw [H * D]; then the first `nrot` entries of every head are rotated
+// (entry 2i with 2i+1, angle pos * inv_freq[i]) and the row is stored in place.  The key row (G * D values, kw) gets
+// the same treatment on its way into the slot's cache row, the values are copied behind it.  k == nullptr: a layer
+// that borrows another layer's keys and values prepares its queries only.  Norm and rotation are fp32; a value is
+// rounded once, after the rotation.  A thread owns both members of a rotated pair, so in-place stores race with no load.
+template <typename T>
+__global__ void full_norm_append_kernel(T* __restrict__ q, long long q_stride, const T* __restrict__ k, long long k_stride,
+                                        const T* __restrict__ v, long long v_stride, const float* __restrict__ inv_freq,
+                                        T* __restrict__ cache, long long slot_stride, const int* __restrict__ meta,
+                                        const int* __restrict__ tok_seq, int H, int G, int D, int V, int nrot, float eps,
+                                        const T* __restrict__ qw, const T* __restrict__ kw) {
+  __shared__ float red[33];
+  int t = blockIdx.x;
+  const int* m = meta + 4 * tok_seq[t];
+  int pos = m[3] + (t - m[0]);
+  float fpos = (float)pos;
+  for (int part = 0; part < (k ? 2 : 1); ++part) {
+    const T* src = part == 0 ? q + (size_t)t * q_stride : k + (size_t)t * k_stride;
+    T* dst = part == 0 ? q + (size_t)t * q_stride
+                       : cache + (size_t)m[2] * slot_stride + (size_t)pos * (G * (D + V));
+    const T* w = part == 0 ? qw : kw;
+    int n = (part == 0 ? H : G) * D;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      float x = to_f(src[i]);
+      ss += x * x;
+    }
+    float inv = 1.f / sqrtf(block_sum(ss, red) / n + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      int d = i % D;
+      if (d < nrot) {
+        if (d & 1) continue;  // written by the owner of the even member
+        float a = to_f(src[i]) * inv * to_f(w[i]), b = to_f(src[i + 1]) * inv * to_f(w[i + 1]), sn, cs;
+        sincosf(fpos * inv_freq[d >> 1], &sn, &cs);
+        dst[i] = from_f<T>(a * cs - b * sn);
+        dst[i + 1] = from_f<T>(b * cs + a * sn);
+      } else {
+        dst[i] = from_f<T>(to_f(src[i]) * inv * to_f(w[i]));
+      }
+    }
+  }
+  if (k) {
+    const T* vs = v + (size_t)t * v_stride;
+    T* vd = cache + (size_t)m[2] * slot_stride + (size_t)pos * (G * (D + V)) + (size_t)G * D;
+    for (int i = threadIdx.x; i < G * V; i += blockDim.x) vd[i] = vs[i];
+  }
+}
+
+// Fixed-decay linear recurrence, token by token: S <- lam_h S + k v^T, o = S^T q, per head, S [D, V] fp32 in the slot.
+// Grid (sequence, head, 32-column tile of V); thread (lane, dg) keeps S[dg + 8 i][v0 + lane] in registers (D <= 256),
+// the eight row groups' partial read-outs meet in shared memory.  The form for one-token steps and short portions;
+// o is written raw (fp32 [N, H * V]): the norm over all heads and the gate follow in norm_gate_rows_kernel.
+#define LS_MAXI 32
+template <typename T>
+__global__ void __launch_bounds__(256) lightning_scan_kernel(const T* __restrict__ q, long long q_stride,
+                                                             const T* __restrict__ k, long long k_stride,
+                                                             const T* __restrict__ v, long long v_stride,
+                                                             const float* __restrict__ decay, float* __restrict__ state,
+                                                             const int* __restrict__ meta, float* __restrict__ oraw,
+                                                             int H, int D, int V) {
+  __shared__ float qs[256], ks[256], part[8][33];
+  const int* m = meta + 4 * blockIdx.x;
+  int r0 = m[0], n = m[1], slot = m[2];
+  int h = blockIdx.y, v0 = blockIdx.z * 32;
+  int lane = threadIdx.x & 31, dg = threadIdx.x >> 5;
+  int vc = v0 + lane;
+  bool live = vc < V;
+  float lam = decay[h];
+  float* sp = state + (((size_t)slot * H + h) * D) * V;
+  float S[LS_MAXI];
+#pragma unroll
+  for (int i = 0; i < LS_MAXI; ++i) {
+    int d = dg + 8 * i;
+    S[i] = d < D && live ? sp[(size_t)d * V + vc] : 0.f;
+  }
+  for (int t = r0; t < r0 + n; ++t) {
+    for (int d = threadIdx.x; d < D; d += 256) {
+      qs[d] = to_f(q[(size_t)t * q_stride + (size_t)h * D + d]);
+      ks[d] = to_f(k[(size_t)t * k_stride + (size_t)h * D + d]);
+    }
+    float vv = live ? to_f(v[(size_t)t * v_stride + (size_t)h * V + vc]) : 0.f;
+    __syncthreads();
+    float o = 0.f;
+#pragma unroll
+    for (int i = 0; i < LS_MAXI; ++i) {
+      int d = dg + 8 * i;
+      if (d < D) {
+        S[i] = lam * S[i] + ks[d] * vv;
+        o += S[i] * qs[d];
+      }
+    }
+    part[dg][lane] = o;
+    __syncthreads();
+    if (dg == 0 && live) {
+      float a = 0.f;
+#pragma unroll
+      for (int g = 0; g < 8; ++g) a += part[g][lane];
+      oraw[(size_t)t * H * V + (size_t)h * V + vc] = a;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < LS_MAXI; ++i) {
+      int d = dg + 8 * i;
+      if (d < D) sp[(size_t)d * V + vc] = S[i];
+    }
+  }
+}
+
+// The same recurrence over a prompt portion in chunks of LC_L = 64 tokens.  With S the state before the chunk and
+// positions t, s counted inside it,
+//   o_t = lam^(t+1) S^T q_t + sum_{s <= t} lam^(t-s) (q_t . k_s) v_s          S' = lam^len S + sum_s lam^(len-1-s) k_s v_s^T
+// so a chunk is four small matrix products (scores, weighted values, read-out of the old state, state update) instead
+// of 64 dependent steps; powers of lam only have non-negative exponents, so nothing overflows however small lam is.
+// Grid (sequence, head, 32-column tile of V), 256 threads, everything fp32 in shared memory: Q and K of the chunk
+// transposed ([D][68]), the decayed causal scores transposed ([s][t]), the V tile, the state tile [D][32].
+// The scores are recomputed by each column tile of a head; they are a small part of the chunk's arithmetic.
+#define LC_L 64
+#define LC_LP 68
+#define LC_VT 32
+template <typename T>
+__global__ void __launch_bounds__(256) lightning_chunk_kernel(const T* __restrict__ q, long long q_stride,
+                                                              const T* __restrict__ k, long long k_stride,
+                                                              const T* __restrict__ v, long long v_stride,
+                                                              const float* __restrict__ decay, float* __restrict__ state,
+                                                              const int* __restrict__ meta, float* __restrict__ oraw,
+                                                              int H, int D, int V) {
+  extern __shared__ __align__(16) float lsm[];
+  float* Qt = lsm;                       // [D][LC_LP]
+  float* Kt = Qt + (size_t)D * LC_LP;    // [D][LC_LP]
+  float* At = Kt + (size_t)D * LC_LP;    // [LC_L][LC_LP]: At[s][t] = lam^(t-s) q_t . k_s for s <= t, else 0
+  float* Vs = At + LC_L * LC_LP;         // [LC_L][LC_VT]
+  float* Ss = Vs + LC_L * LC_VT;         // [D][LC_VT]
+  float* pw = Ss + (size_t)D * LC_VT;    // [LC_L + 1]: lam^i
+  const int* m = meta + 4 * blockIdx.x;
+  int r0 = m[0], n = m[1], slot = m[2];
+  int h = blockIdx.y, v0 = blockIdx.z * LC_VT;
+  int tid = threadIdx.x, lane = tid & 31, tg = tid >> 5;
+  int vc = v0 + lane;
+  bool live = vc < V;
+  float* sp = state + (((size_t)slot * H + h) * D) * V;
+  for (int i = tid; i <= LC_L; i += 256) pw[i] = (float)pow((double)decay[h], (double)i);
+  for (int i = tid; i < D * LC_VT; i += 256) {
+    int d = i >> 5, c = i & 31;
+    Ss[i] = v0 + c < V ? sp[(size_t)d * V + v0 + c] : 0.f;
+  }
+  int ty = tid >> 4, tx = tid & 15;
+  for (int c0 = 0; c0 < n; c0 += LC_L) {
+    int len = min(LC_L, n - c0);
+    __syncthreads();  // the previous chunk is done with every tile; pw and Ss are written
+    for (int i = tid; i < LC_L * D; i += 256) {
+      int t = i / D, d = i - t * D;
+      size_t row = (size_t)(r0 + c0 + t);
+      Qt[d * LC_LP + t] = t < len ? to_f(q[row * q_stride + (size_t)h * D + d]) : 0.f;
+      Kt[d * LC_LP + t] = t < len ? to_f(k[row * k_stride + (size_t)h * D + d]) : 0.f;
+    }
+    for (int i = tid; i < LC_L * LC_VT; i += 256) {
+      int t = i >> 5, c = i & 31;
+      Vs[i] = t < len && v0 + c < V ? to_f(v[(size_t)(r0 + c0 + t) * v_stride + (size_t)h * V + v0 + c]) : 0.f;
+    }
+    __syncthreads();
+    {  // scores: thread (ty, tx) owns t = 4 ty .. 4 ty + 3 against s = 4 tx .. 4 tx + 3
+      float a[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) a[i][j] = 0.f;
+      if (tx <= ty) {  // blocks above the diagonal hold no visible pair
+        for (int d = 0; d < D; ++d) {
+          float4 qv = *reinterpret_cast<const float4*>(Qt + d * LC_LP + 4 * ty);
+          float4 kv = *reinterpret_cast<const float4*>(Kt + d * LC_LP + 4 * tx);
+          const float qa[4] = {qv.x, qv.y, qv.z, qv.w}, ka[4] = {kv.x, kv.y, kv.z, kv.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) a[i][j] += qa[i] * ka[j];
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        int s = 4 * tx + j;
+        float o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          int t = 4 * ty + i;
+          o[i] = s <= t ? a[i][j] * pw[t - s] : 0.f;
+        }
+        *reinterpret_cast<float4*>(At + s * LC_LP + 4 * ty) = make_float4(o[0], o[1], o[2], o[3]);
+      }
+    }
+    __syncthreads();
+    {  // outputs: thread (lane, tg) owns column v0 + lane of rows t = 8 tg .. 8 tg + 7
+      float in[8], st[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) in[i] = st[i] = 0.f;
+      int smax = min(len, 8 * tg + 8);
+      for (int s = 0; s < smax; ++s) {
+        float vv = Vs[s * LC_VT + lane];
+        float4 a0 = *reinterpret_cast<const float4*>(At + s * LC_LP + 8 * tg);
+        float4 a1 = *reinterpret_cast<const float4*>(At + s * LC_LP + 8 * tg + 4);
+        in[0] += a0.x * vv; in[1] += a0.y * vv; in[2] += a0.z * vv; in[3] += a0.w * vv;
+        in[4] += a1.x * vv; in[5] += a1.y * vv; in[6] += a1.z * vv; in[7] += a1.w * vv;
+      }
+      for (int d = 0; d < D; ++d) {
+        float sv = Ss[d * LC_VT + lane];
+        float4 q0 = *reinterpret_cast<const float4*>(Qt + d * LC_LP + 8 * tg);
+        float4 q1 = *reinterpret_cast<const float4*>(Qt + d * LC_LP + 8 * tg + 4);
+        st[0] += q0.x * sv; st[1] += q0.y * sv; st[2] += q0.z * sv; st[3] += q0.w * sv;
+        st[4] += q1.x * sv; st[5] += q1.y * sv; st[6] += q1.z * sv; st[7] += q1.w * sv;
+      }
+      if (live) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          int t = 8 * tg + i;
+          if (t < len) oraw[(size_t)(r0 + c0 + t) * H * V + (size_t)h * V + vc] = in[i] + pw[t + 1] * st[i];
+        }
+      }
+    }
+    __syncthreads();
+    // the values as the state update wants them: v_s lam^(len-1-s)
+    for (int i = tid; i < LC_L * LC_VT; i += 256) {
+      int s = i >> 5;
+      Vs[i] = s < len ? Vs[i] * pw[len - 1 - s] : 0.f;
+    }
+    __syncthreads();
+    {  // state: thread (lane, tg) owns column lane of rows d = tg + 8 i, four rows at a time
+      float lend = pw[len];
+      for (int i0 = 0; tg + 8 * i0 < D; i0 += 4) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        int dd[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) dd[u] = min(tg + 8 * (i0 + u), D - 1);  // rows past D: computed, not stored
+        for (int s = 0; s < len; s += 4) {  // rows of Kt are zero past len
+          float w0 = Vs[s * LC_VT + lane], w1 = Vs[(s + 1) * LC_VT + lane], w2 = Vs[(s + 2) * LC_VT + lane],
+                w3 = Vs[(s + 3) * LC_VT + lane];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            float4 kv = *reinterpret_cast<const float4*>(Kt + dd[u] * LC_LP + s);
+            acc[u] += kv.x * w0 + kv.y * w1 + kv.z * w2 + kv.w * w3;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          int d = tg + 8 * (i0 + u);
+          if (d < D) Ss[d * LC_VT + lane] = lend * Ss[d * LC_VT + lane] + acc[u];
+        }
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < D * LC_VT; i += 256) {
+    int d = i >> 5, c = i & 31;
+    if (v0 + c < V) sp[(size_t)d * V + v0 + c] = Ss[i];
+  }
+}
+
+// out[r, c] = o[r, c] / sqrt(mean_c(o[r, :]^2) + eps) * w[c] * sigmoid(g[r, c]): the RMS norm over ALL heads'
+// concatenated read-outs (fp32 in) with its weight and the output gate, rounded once to the activation type.
+template <typename T>
+__global__ void norm_gate_rows_kernel(const float* __restrict__ o, const T* __restrict__ w, const T* __restrict__ g,
+                                      long long g_stride, T* __restrict__ out, int n, float eps) {
+  __shared__ float red[33];
+  size_t r = blockIdx.x;
+  const float* src = o + r * n;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) ss += src[i] * src[i];
+  float inv = 1.f / sqrtf(block_sum(ss, red) / n + eps);
+  for (int i = threadIdx.x; i < n; i += blockDim.x)
+    out[r * n + i] = from_f<T>(src[i] * inv * to_f(w[i]) * sigmoidf_(to_f(g[r * g_stride + i])));
+}
+
+// resid[r] += norm(a[r] + sigmoid(sg[r]) * b[r]) * w: the post-norm of a feed-forward whose always-on branch b is
+// weighed by one sigmoid gate per token, and the residual sum, in one pass (fp32 arithmetic; b and sg optional).
+// kind 0: layer norm without bias, 1: RMS norm.
+template <typename T>
+__global__ void gated_sum_norm_kernel(const T* __restrict__ a, long long a_stride, const T* __restrict__ b,
+                                      long long b_stride, const T* __restrict__ sg, long long sg_stride,
+                                      const T* __restrict__ w, float* __restrict__ resid, long long r_stride, int n,
+                                      float eps, int kind) {
+  __shared__ float red[33];
+  size_t r = blockIdx.x;
+  float gt = b ? (sg ? sigmoidf_(to_f(sg[r * sg_stride])) : 1.f) : 0.f;
+  float mean = 0.f;
+  if (kind == 0) {
+    float s = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) s += to_f(a[r * a_stride + i]) + (b ? gt * to_f(b[r * b_stride + i]) : 0.f);
+    mean = block_sum(s, red) / n;
+  }
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float y = to_f(a[r * a_stride + i]) + (b ? gt * to_f(b[r * b_stride + i]) : 0.f) - mean;
+    ss += y * y;
+  }
+  float inv = 1.f / sqrtf(block_sum(ss, red) / n + eps);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float y = to_f(a[r * a_stride + i]) + (b ? gt * to_f(b[r * b_stride + i]) : 0.f) - mean;
+    resid[r * r_stride + i] += y * inv * to_f(w[i]);
+  }
+}
+
+}  // namespace hyb
+
+extern "C" {
+
+int hyb_full_norm_append(void* q, long long q_stride, const void* k, long long k_stride, const void* v, long long v_stride,
+                         const float* inv_freq, void* cache, long long slot_stride, const int* meta, const int* tok_seq,
+                         int N, int H, int G, int D, int V, int nrot, float eps, const void* qw, const void* kw, int dt,
+                         cudaStream_t st) {
+  if (N == 0) return 0;
+  if (nrot > D || (nrot & 1) || (nrot > 0 && !inv_freq) || !qw || (k && (!kw || !v || !cache))) return -2;
+  HYB_DISPATCH(dt,
+               (full_norm_append_kernel<bf16><<<N, 256, 0, st>>>((bf16*)q, q_stride, (const bf16*)k, k_stride, (const bf16*)v,
+                                                                 v_stride, inv_freq, (bf16*)cache, slot_stride, meta, tok_seq,
+                                                                 H, G, D, V, nrot, eps, (const bf16*)qw, (const bf16*)kw)),
+               (full_norm_append_kernel<float><<<N, 256, 0, st>>>((float*)q, q_stride, (const float*)k, k_stride,
+                                                                  (const float*)v, v_stride, inv_freq, (float*)cache,
+                                                                  slot_stride, meta, tok_seq, H, G, D, V, nrot, eps,
+                                                                  (const float*)qw, (const float*)kw)));
+  return (int)cudaGetLastError();
+}
+
+// variant 1: token scan; 2: chunks of 64 tokens.  decay [H] fp32 on the device; oraw [N, H * V] fp32.
+int hyb_lightning(const void* q, long long q_stride, const void* k, long long k_stride, const void* v, long long v_stride,
+                  const float* decay, float* state, const int* meta, float* oraw, int nseq, int H, int D, int V,
+                  int variant, int dt, cudaStream_t st) {
+  if (nseq == 0) return 0;
+  if (D < 1 || D > 8 * LS_MAXI || V < 1) return -3;
+  dim3 grid(nseq, H, (V + 31) / 32);
+  if (variant == 1) {
+    HYB_DISPATCH(dt,
+                 (lightning_scan_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)q, q_stride, (const bf16*)k, k_stride,
+                                                                    (const bf16*)v, v_stride, decay, state, meta, oraw, H, D, V)),
+                 (lightning_scan_kernel<float><<<grid, 256, 0, st>>>((const float*)q, q_stride, (const float*)k, k_stride,
+                                                                     (const float*)v, v_stride, decay, state, meta, oraw, H, D, V)));
+    return (int)cudaGetLastError();
+  }
+  if (variant != 2) return -3;
+  size_t smem = ((size_t)2 * D * LC_LP + (size_t)LC_L * LC_LP + (size_t)LC_L * LC_VT + (size_t)D * LC_VT + LC_L + 1 + 3) * sizeof(float);
+  if (smem > 220 * 1024) return -3;
+  cudaError_t e;
+  if (dt == 0) {
+    if ((e = cudaFuncSetAttribute(lightning_chunk_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
+    lightning_chunk_kernel<bf16><<<grid, 256, smem, st>>>((const bf16*)q, q_stride, (const bf16*)k, k_stride, (const bf16*)v,
+                                                          v_stride, decay, state, meta, oraw, H, D, V);
+  } else {
+    if ((e = cudaFuncSetAttribute(lightning_chunk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
+    lightning_chunk_kernel<float><<<grid, 256, smem, st>>>((const float*)q, q_stride, (const float*)k, k_stride,
+                                                           (const float*)v, v_stride, decay, state, meta, oraw, H, D, V);
+  }
+  return (int)cudaGetLastError();
+}
+
+int hyb_norm_gate_rows(const float* o, const void* w, const void* g, long long g_stride, void* out, int rows, int n,
+                       float eps, int dt, cudaStream_t st) {
+  if (rows == 0) return 0;
+  HYB_DISPATCH(dt, (norm_gate_rows_kernel<bf16><<<rows, 256, 0, st>>>(o, (const bf16*)w, (const bf16*)g, g_stride, (bf16*)out, n, eps)),
+               (norm_gate_rows_kernel<float><<<rows, 256, 0, st>>>(o, (const float*)w, (const float*)g, g_stride, (float*)out, n, eps)));
+  return (int)cudaGetLastError();
+}
+
+int hyb_gated_sum_norm(const void* a, long long a_stride, const void* b, long long b_stride, const void* sg,
+                       long long sg_stride, const void* w, float* resid, long long r_stride, int rows, int n, float eps,
+                       int kind, int dt, cudaStream_t st) {
+  if (rows == 0) return 0;
+  if (kind < 0 || kind > 1 || !w) return -3;
+  HYB_DISPATCH(dt,
+               (gated_sum_norm_kernel<bf16><<<rows, 256, 0, st>>>((const bf16*)a, a_stride, (const bf16*)b, b_stride,
+                                                                  (const bf16*)sg, sg_stride, (const bf16*)w, resid, r_stride,
+                                                                  n, eps, kind)),
+               (gated_sum_norm_kernel<float><<<rows, 256, 0, st>>>((const float*)a, a_stride, (const float*)b, b_stride,
+                                                                   (const float*)sg, sg_stride, (const float*)w, resid,
+                                                                   r_stride, n, eps, kind)));
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"
+
+namespace hyb {
+// out[r, c] = silu(in[r, c]) for rows that are a column slice of a wider matrix (row stride in_stride); out is dense.
+template <typename T>
+__global__ void silu_rows_kernel(const T* __restrict__ in, long long in_stride, T* __restrict__ out, int n, long long total) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  long long r = i / n;
+  int c = (int)(i - r * n);
+  out[i] = from_f<T>(siluf_(to_f(in[(size_t)r * in_stride + c])));
+}
+}  // namespace hyb
+
+extern "C" int hyb_silu_rows(const void* in, long long in_stride, void* out, int rows, int n, int dt, cudaStream_t st) {
+  long long total = (long long)rows * n;
+  if (total == 0) return 0;
+  unsigned blocks = (unsigned)((total + 255) / 256);
+  HYB_DISPATCH(dt, (silu_rows_kernel<bf16><<<blocks, 256, 0, st>>>((const bf16*)in, in_stride, (bf16*)out, n, total)),
+               (silu_rows_kernel<float><<<blocks, 256, 0, st>>>((const float*)in, in_stride, (float*)out, n, total)));
+  return (int)cudaGetLastError();
+}

@@ -27,9 +27,10 @@ import torch.nn.functional as F
 from . import build as _build
 
 __all__ = ["BatchPlan", "HybridOpsError", "lib", "embed_rows", "cast_into", "norm_rows", "norm_accumulate", "gelu_",
-           "headmajor_gate", "softcap", "latent_append", "latent_attn", "causal_softmax", "matmul_f32", "conv_silu", "gated_recurrence", "linear",
+           "headmajor_gate", "softcap", "silu_rows", "glu", "latent_append", "latent_attn", "causal_softmax", "matmul_f32", "conv_silu", "gated_recurrence", "linear",
            "rotary_inv_freq", "scaled_inv_freq", "linear_f32", "grouped_linear", "window_append", "window_attn", "head_gate", "relu2_",
-           "token_side_gate", "router_topk", "moe_gemv", "gather_scale_rows", "combine_rows", "act_mul", "scaled_branches"]
+           "token_side_gate", "router_topk", "moe_gemv", "gather_scale_rows", "combine_rows", "act_mul", "scaled_branches",
+           "full_norm_append", "lightning_recurrence", "norm_gate_rows", "gated_sum_norm_accumulate"]
 
 
 class HybridOpsError(RuntimeError):
@@ -59,26 +60,31 @@ def lib() -> ctypes.CDLL:
     vp, i32, i64, f32 = c_void_p, c_int, c_longlong, c_float
     h.hyb_error_string.restype = ctypes.c_char_p
     h.hyb_error_string.argtypes = [i32]
-    h.hyb_embed_rows.argtypes = [vp, vp, vp, i32, i32, vp, vp, vp, i32, vp]
+    h.hyb_embed_rows.argtypes = [vp, vp, vp, i32, i32, vp, vp, vp, f32, i32, vp]
     h.hyb_cast_rows.argtypes = [vp, i64, i32, vp, i64, i32, i32, i32, vp]
     h.hyb_norm_rows.argtypes = [vp, i64, i32, vp, vp, i32, vp, i64, i32, i32, i32, f32, i32, i32, f32, f32, vp]
     h.hyb_gelu_rows.argtypes = [vp, i64, i32, i32, vp]
+    h.hyb_silu_rows.argtypes = [vp, i64, vp, i32, i32, i32, vp]
     h.hyb_window_append.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp, vp, i64, vp, i32, vp]
-    h.hyb_window_attn.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, i32, vp, vp, i32, i32, i32, i32, vp]
+    h.hyb_window_attn.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, i32, vp, vp, i32, i32, i32, f32, vp, i32, vp]
     h.hyb_head_gate.argtypes = [vp, vp, i64, vp, i32, i32, i32, i32, vp]
     h.hyb_token_side_gate.argtypes = [vp, i64, vp, i64, i32, vp, vp, i32, i32, i32, vp]
-    h.hyb_router_topk.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
-    h.hyb_moe_up.argtypes = [vp, i64, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp]
-    h.hyb_moe_down.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]
+    h.hyb_router_topk.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp, vp]
+    h.hyb_moe_up.argtypes = [vp, i64, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp]
+    h.hyb_moe_down.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, i64, i32, vp]
     h.hyb_gather_scale_rows.argtypes = [vp, i64, vp, vp, vp, i32, i32, i32, vp]
-    h.hyb_combine_rows.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, vp]
-    h.hyb_act_mul_rows.argtypes = [vp, i64, vp, i64, i32, i32, i32, vp]
+    h.hyb_combine_rows.argtypes = [vp, vp, vp, vp, i32, i32, i32, vp, i32, vp, i64, i32, vp]
+    h.hyb_act_mul_rows.argtypes = [vp, i64, vp, i64, i32, i32, f32, i32, vp]
     h.hyb_scaled_branches.argtypes = [vp, i64, vp, i64, vp, vp, i64, vp, i64, vp, i32, i32, i32, vp]
     h.hyb_headmajor_gate.argtypes = [vp, vp, i64, vp, i32, i32, i32, i32, vp]
     h.hyb_softcap.argtypes = [vp, vp, i64, f32, i32, vp]
     h.hyb_latent_append.argtypes = [vp, i64, vp, i64, vp, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp]
     h.hyb_latent_attn.argtypes = [vp, vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp, vp, i32, vp]
-    h.hyb_causal_softmax.argtypes = [vp, vp, i64, i32, i32, i32, f32, i32, i32, i32, i32, i32, vp]
+    h.hyb_causal_softmax.argtypes = [vp, vp, i64, i32, i32, i32, f32, i32, i32, i32, i32, f32, vp, i32, i32, vp]
+    h.hyb_full_norm_append.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp, i32, vp]
+    h.hyb_lightning.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]
+    h.hyb_norm_gate_rows.argtypes = [vp, vp, vp, i64, vp, i32, i32, f32, i32, vp]
+    h.hyb_gated_sum_norm.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, i64, i32, i32, f32, i32, i32, vp]
     h.hyb_conv_silu.argtypes = [vp, i64, vp, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, vp]
     h.hyb_gated_recurrence.argtypes = [ctypes.POINTER(_RecArgs), i32, i32, i32, i32, vp, vp, vp, vp]
     _lib = h
@@ -199,11 +205,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None) -
 # rows
 # ---------------------------------------------------------------------------------------------------------
 def embed_rows(table: torch.Tensor, tokens: torch.Tensor, pos_table: Optional[torch.Tensor] = None,
-               plan: Optional["BatchPlan"] = None) -> torch.Tensor:
-    """fp32 rows of ``table`` for int32 ``tokens [N]``; with ``pos_table [positions, width]`` the learned vector of each
-    token's position in its sequence (from ``plan``) is added, unscaled, in fp32."""
+               plan: Optional["BatchPlan"] = None, scale: float = 1.0) -> torch.Tensor:
+    """fp32 rows of ``table`` for int32 ``tokens [N]``, times ``scale``; with ``pos_table [positions, width]`` the learned
+    vector of each token's position in its sequence (from ``plan``) is added, unscaled, in fp32."""
     if not table.is_cuda:
         x = table[tokens.long()].float()
+        if scale != 1.0:
+            x = x * float(scale)
         return x if pos_table is None else x + pos_table[plan.positions].float()
     x = torch.empty(tokens.numel(), table.size(1), device=table.device, dtype=torch.float32)
     if pos_table is not None and (pos_table.dtype != table.dtype or pos_table.size(1) != table.size(1) or not pos_table.is_contiguous()):
@@ -211,7 +219,7 @@ def embed_rows(table: torch.Tensor, tokens: torch.Tensor, pos_table: Optional[to
     _check(lib().hyb_embed_rows(table.data_ptr(), tokens.data_ptr(), x.data_ptr(), tokens.numel(), table.size(1),
                                 None if pos_table is None else pos_table.data_ptr(),
                                 None if pos_table is None else plan.meta.data_ptr(),
-                                None if pos_table is None else plan.tok_seq.data_ptr(), _dt(table), _st()), "embed_rows")
+                                None if pos_table is None else plan.tok_seq.data_ptr(), float(scale), _dt(table), _st()), "embed_rows")
     return x
 
 
@@ -282,6 +290,16 @@ def gelu_(x: torch.Tensor) -> torch.Tensor:
     assert x.is_contiguous()
     _check(lib().hyb_gelu_rows(x.data_ptr(), x.numel(), _dt(x), 0, _st()), "gelu")
     return x
+
+
+def silu_rows(x: torch.Tensor) -> torch.Tensor:
+    """``silu(x)`` of rows that may be a column slice of a wider matrix, evaluated in fp32; the result is dense."""
+    if not x.is_cuda:
+        return F.silu(x.float()).to(x.dtype)
+    xs, n = _rows(x)
+    out = torch.empty(x.size(0), n, device=x.device, dtype=x.dtype)
+    _check(lib().hyb_silu_rows(x.data_ptr(), xs, out.data_ptr(), x.size(0), n, _dt(x), _st()), "silu_rows")
+    return out
 
 
 def relu2_(x: torch.Tensor) -> torch.Tensor:
@@ -417,14 +435,18 @@ def latent_attn(qlat: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, plan: 
 
 
 def causal_softmax(scores: torch.Tensor, first_pos: int, scale: float, out_dtype: torch.dtype, window: int = 0,
-                   key0: int = 0, sink: bool = False, split: bool = False) -> torch.Tensor:
+                   key0: int = 0, sink: bool = False, split: bool = False, cap: float = 0.0,
+                   sink_vals: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``softmax(scale * scores)`` over the visible keys of fp32 ``scores [heads, rows, keys]``: row ``i`` is position
     ``first_pos + i``, column ``j`` is position ``key0 + j``; a key is visible when it is not later than the row and,
     with ``window > 0``, fewer than ``window`` positions back.  Hidden keys get probability 0.  Result in ``out_dtype``.
     ``sink``: the denominator gains one slot of score zero that has no value, ``p_j = e^{s_j} / (1 + sum_k e^{s_k})``.
     ``split``: the result is ``[heads, rows, 2 * keys]``: the weights rounded to ``out_dtype`` and, behind them, what the
     rounding dropped (``p - round(p)``, rounded again).  A product with the values stacked twice then sums the weights to
-    twice the mantissa of ``out_dtype`` on the tensor cores."""
+    twice the mantissa of ``out_dtype`` on the tensor cores.
+    ``cap > 0``: a scaled score ``s`` becomes ``cap * tanh(s / cap)``.  ``sink_vals`` (fp32 ``[heads]``, with ``sink``): the
+    sink's score is a learned number per head instead of zero (neither scaled nor capped); the leading axis of
+    ``scores`` runs over (anything, head) with the head innermost."""
     Hh, n, keys = scores.shape
     if not scores.is_cuda:
         j = key0 + torch.arange(keys)
@@ -432,9 +454,15 @@ def causal_softmax(scores: torch.Tensor, first_pos: int, scale: float, out_dtype
         hidden = j[None, None, :] > pi
         if window > 0:
             hidden = hidden | (pi - j[None, None, :] >= window)
-        sc = (scores.float() * scale).masked_fill(hidden, float("-inf"))
+        sc = scores.float() * scale
+        if cap > 0:
+            sc = cap * torch.tanh(sc / cap)
+        sc = sc.masked_fill(hidden, float("-inf"))
         if sink:
-            sc = torch.cat((sc, sc.new_zeros(Hh, n, 1)), -1)
+            col = sc.new_zeros(Hh, n, 1)
+            if sink_vals is not None:
+                col = col + sink_vals.float().repeat(Hh // sink_vals.numel())[:, None, None]
+            sc = torch.cat((sc, col), -1)
         pr = torch.softmax(sc, -1)[..., :keys]
         if split:
             hi = pr.to(out_dtype)
@@ -442,9 +470,13 @@ def causal_softmax(scores: torch.Tensor, first_pos: int, scale: float, out_dtype
         return pr.to(out_dtype)
     if scores.dtype != torch.float32 or not scores.is_contiguous():
         raise HybridOpsError("scores are dense fp32")
+    if sink_vals is not None and (sink_vals.dtype != torch.float32 or not sink_vals.is_contiguous() or Hh % sink_vals.numel()):
+        raise HybridOpsError("sink scores are dense fp32, one per head")
     p = torch.empty(Hh, n, 2 * keys if split else keys, device=scores.device, dtype=out_dtype)
     _check(lib().hyb_causal_softmax(scores.data_ptr(), p.data_ptr(), Hh * n, n, keys, int(first_pos), float(scale),
-                                    int(window), int(key0), int(bool(sink)), int(bool(split)), _dt(p), _st()), "causal_softmax")
+                                    int(window), int(key0), int(bool(sink)), int(bool(split)), float(cap),
+                                    None if sink_vals is None else sink_vals.data_ptr(),
+                                    0 if sink_vals is None else sink_vals.numel(), _dt(p), _st()), "causal_softmax")
     return p
 
 
@@ -509,13 +541,15 @@ def visible_from(pos: torch.Tensor, window: int, mask: str) -> torch.Tensor:
 
 
 def window_attn(q: torch.Tensor, g: Optional[torch.Tensor], cache: torch.Tensor, plan: BatchPlan, H: int, G: int, D: int,
-                V: int, scale: float, window: int, split: int = 0, mask: str = "window", sink: bool = False) -> torch.Tensor:
+                V: int, scale: float, window: int, split: int = 0, mask: str = "window", sink: bool = False,
+                cap: float = 0.0, sink_vals: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Softmax attention of every token over the cached keys of its slot that are not later than it and (``window > 0``)
     fewer than ``window`` positions back; query head ``h`` reads key/value head ``h // (H/G)``.  Each head's output is
     multiplied by ``sigmoid(g[token, h])`` when ``g [N, H]`` is given, or channel by channel by ``sigmoid(g)`` for
     ``g [N, H*V]``.  ``mask="chunk"``: a token sees the earlier keys of its own block of ``window`` positions (blocks
     numbered from the first position of the sequence) instead of the last ``window``.  ``sink``: the softmax denominator gains
-    one slot of score zero without a value.  Returns ``[N, H*V]``.  The form for one-token steps and
+    one slot of score zero (or of the learned score ``sink_vals[h]``, fp32) without a value.  ``cap > 0``: a scaled score
+    ``s`` becomes ``cap * tanh(s / cap)``.  Returns ``[N, H*V]``.  The form for one-token steps and
     short portions: one block per token and key/value head, the cache tile shared by the group's query heads.
     ``split`` (CUDA): key shares per token, 0 = chosen from the batch shape and the window alone, so that a captured
     step stays valid while contexts grow."""
@@ -529,12 +563,15 @@ def window_attn(q: torch.Tensor, g: Optional[torch.Tensor], cache: torch.Tensor,
             vv = rows[:, G * D:].reshape(-1, G, V).repeat_interleave(rep, 1)
             qq = q[r0:r0 + n].float().reshape(n, H, D)
             s = torch.einsum("nhd,khd->hnk", qq, kk) * scale
+            if cap > 0:
+                s = cap * torch.tanh(s / cap)
             pi = (p0 + torch.arange(n))[None, :, None]
             j = torch.arange(p0 + n)[None, None, :]
             hid = (j > pi) | (j < visible_from(pi, window, mask))
             s = s.masked_fill(hid, float("-inf"))
             if sink:
-                s = torch.cat((s, s.new_zeros(H, n, 1)), -1)
+                col = s.new_zeros(H, n, 1) if sink_vals is None else sink_vals.float()[:, None, None].expand(H, n, 1)
+                s = torch.cat((s, col), -1)
             o = torch.einsum("hnk,khv->nhv", torch.softmax(s, -1)[..., :p0 + n], vv)
             if g is not None and g.size(1) == H * V and V != 1:
                 o = o * torch.sigmoid(g[r0:r0 + n].float()).view(n, H, V)
@@ -544,6 +581,8 @@ def window_attn(q: torch.Tensor, g: Optional[torch.Tensor], cache: torch.Tensor,
         return out
     if g is not None and g.size(1) not in (H, H * V):
         raise HybridOpsError("the gate has one column per head or per output channel")
+    if sink_vals is not None and (sink_vals.dtype != torch.float32 or sink_vals.numel() != H or not sink_vals.is_contiguous()):
+        raise HybridOpsError("sink scores are dense fp32, one per head")
     gate_mode = 0 if g is None else (1 if g.size(1) == H else 2)
     out = torch.empty(N, H * V, device=q.device, dtype=q.dtype)
     blocks = N * G
@@ -557,7 +596,8 @@ def window_attn(q: torch.Tensor, g: Optional[torch.Tensor], cache: torch.Tensor,
                                  0 if g is None else _rows(g)[0], cache.data_ptr(), cache.stride(0), plan.meta.data_ptr(),
                                  plan.tok_seq.data_ptr(), out.data_ptr(), N, H, G, D, V, float(scale), int(window), nsplit,
                                  None if pa is None else pa.data_ptr(), None if pm is None else pm.data_ptr(),
-                                 _MASK_KINDS[mask if window > 0 else "window"], int(bool(sink)), gate_mode, _dt(q), _st()),
+                                 _MASK_KINDS[mask if window > 0 else "window"], int(bool(sink)), gate_mode, float(cap),
+                                 None if sink_vals is None else sink_vals.data_ptr(), _dt(q), _st()),
            "window_attn")  # no mask size: every earlier position, whichever kind
     return out
 
@@ -565,15 +605,24 @@ def window_attn(q: torch.Tensor, g: Optional[torch.Tensor], cache: torch.Tensor,
 # ---------------------------------------------------------------------------------------------------------
 # mixture of experts: sigmoid router, top-k choice, experts applied to the weighted input
 # ---------------------------------------------------------------------------------------------------------
-_ROUTER_MODES = {"sigmoid": 0, "softmax": 1}
+_ROUTER_MODES = {"sigmoid": 0, "softmax": 1, "softmax_all": 2}
 
 
-def router_topk(z: torch.Tensor, top: int, mode: str = "sigmoid") -> Tuple[torch.Tensor, torch.Tensor]:
+def router_topk(z: torch.Tensor, top: int, mode: str = "sigmoid",
+                correction: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """From fp32 router logits ``z [N, E]``: the ``top`` experts with the largest logits per token (ties go to the lower
     index) as int32 ``[N, top]`` and their scores as fp32 ``[N, top]``: ``sigmoid(z)`` of each, not renormalised
-    (``mode="sigmoid"``), or the softmax restricted to the selected logits (``mode="softmax"``)."""
+    (``mode="sigmoid"``), or the softmax restricted to the selected logits (``mode="softmax"``).
+    ``mode="softmax_all"``: scores ``s`` are the softmax over ALL logits; the ``top`` largest ``s + correction`` are chosen
+    (``correction`` fp32 ``[E]``, optional) and the result is the chosen ``s`` divided by their sum ``+ 1e-20``."""
     N, E = z.shape
     if not z.is_cuda:
+        if mode == "softmax_all":
+            s = torch.softmax(z.float(), -1)
+            choice = s if correction is None else s + correction.float()
+            idx = torch.argsort(-choice, dim=-1, stable=True)[:, :top]
+            w = torch.gather(s, 1, idx)
+            return idx.to(torch.int32), w / (w.sum(-1, keepdim=True) + 1e-20)
         if mode == "softmax":
             idx = torch.argsort(-z.float(), dim=-1, stable=True)[:, :top]
             return idx.to(torch.int32), torch.softmax(torch.gather(z.float(), 1, idx), -1)
@@ -584,17 +633,29 @@ def router_topk(z: torch.Tensor, top: int, mode: str = "sigmoid") -> Tuple[torch
         raise HybridOpsError("router logits are dense fp32")
     idx = torch.empty(N, top, device=z.device, dtype=torch.int32)
     wt = torch.empty(N, top, device=z.device, dtype=torch.float32)
-    _check(lib().hyb_router_topk(z.data_ptr(), idx.data_ptr(), wt.data_ptr(), N, E, int(top), _ROUTER_MODES[mode], _st()),
-           "router_topk")
+    if correction is not None and (correction.dtype != torch.float32 or correction.numel() != E or not correction.is_contiguous()):
+        raise HybridOpsError("the router's correction is dense fp32, one number per output")
+    _check(lib().hyb_router_topk(z.data_ptr(), idx.data_ptr(), wt.data_ptr(), N, E, int(top), _ROUTER_MODES[mode],
+                                 None if correction is None else correction.data_ptr(), _st()), "router_topk")
     return idx, wt
 
 
+def glu(g: torch.Tensor, u: torch.Tensor, act: str = "silu", limit: float = 0.0) -> torch.Tensor:
+    """The product of a gated feed-forward from its fp32 gate and up pre-activations: ``silu(g) u``, ``gelu_tanh(g) u``, or
+    ``act="clamped"``: ``g' sigmoid(1.702 g') (u' + 1)`` with ``g' = min(g, limit)``, ``u' = clamp(u, -limit, limit)``."""
+    if act == "clamped":
+        g = torch.clamp(g, max=limit)
+        return g * torch.sigmoid(1.702 * g) * (torch.clamp(u, -limit, limit) + 1.0)
+    return (F.silu(g) if act == "silu" else F.gelu(g, approximate="tanh")) * u
+
+
 def moe_gemv(h: torch.Tensor, idx: torch.Tensor, wt: torch.Tensor, up: torch.Tensor, down: torch.Tensor,
-             gated: bool = False) -> torch.Tensor:
+             gated: bool = False, act: str = "silu", limit: float = 0.0) -> torch.Tensor:
     """Experts read by index, per token.  ``gated=False``: ``sum_k down[e_k] relu(up[e_k] (w_k h))^2`` (``up [E, ff, C]``:
     the score scales the expert's input).  ``gated=True``: ``sum_k w_k down[e_k] (silu(G h) * (U h))`` with
     ``up [E, 2 ff, C]`` holding an expert's gate rows ``G`` and then its up rows ``U`` (the score weighs the expert's
-    output).  ``down [E, C, ff]``.  The form for few tokens: weight-streaming kernels in which one block serves every
+    output; ``act`` / ``limit`` pick the gated product, see :func:`glu`).  A choice whose index is ``E`` or more is an
+    identity expert: it has no tensors and contributes ``w_k h``.  ``down [E, C, ff]``.  The form for few tokens: weight-streaming kernels in which one block serves every
     token that chose its expert (an expert's weights are read once per step), no sorting and no host synchronisation."""
     N, C = h.shape
     E, ff, _ = up.shape
@@ -606,22 +667,28 @@ def moe_gemv(h: torch.Tensor, idx: torch.Tensor, wt: torch.Tensor, up: torch.Ten
         for t in range(N):
             for k in range(top):
                 e = int(idx[t, k])
+                if e >= E:
+                    out[t] += wt[t, k] * h[t].float()
+                    continue
                 if gated:
                     gu = F.linear(h[t], up[e]).float()
-                    out[t] += wt[t, k] * F.linear((F.silu(gu[:ff]) * gu[ff:]).to(h.dtype), down[e]).float()
+                    out[t] += wt[t, k] * F.linear(glu(gu[:ff], gu[ff:], act, limit).to(h.dtype), down[e]).float()
                     continue
                 xin = (wt[t, k] * h[t].float()).to(h.dtype)
                 a = torch.relu(F.linear(xin, up[e]).float()).square().to(h.dtype)
                 out[t] += F.linear(a, down[e]).float()
         return out.to(h.dtype)
     assert up.is_contiguous() and down.is_contiguous() and idx.is_contiguous() and wt.is_contiguous()
-    act = torch.empty(N, top, ff, device=h.device, dtype=torch.float32)
+    if act not in ("silu", "clamped"):
+        raise HybridOpsError(f"experts by index know the gated products 'silu' and 'clamped', not {act!r}")
+    act_ = torch.empty(N, top, ff, device=h.device, dtype=torch.float32)
     ypair = torch.empty(N, top, C, device=h.device, dtype=torch.float32)
     out = torch.empty(N, C, device=h.device, dtype=h.dtype)
-    _check(lib().hyb_moe_up(h.data_ptr(), _rows(h)[0], idx.data_ptr(), wt.data_ptr(), up.data_ptr(), act.data_ptr(), N, top,
-                            C, ff, E, int(bool(gated)), _dt(h), _st()), "moe_up")
-    _check(lib().hyb_moe_down(act.data_ptr(), idx.data_ptr(), wt.data_ptr() if gated else None, down.data_ptr(),
-                              ypair.data_ptr(), out.data_ptr(), N, top, C, ff, E, _dt(h), _st()), "moe_down")
+    _check(lib().hyb_moe_up(h.data_ptr(), _rows(h)[0], idx.data_ptr(), wt.data_ptr(), up.data_ptr(), act_.data_ptr(), N, top,
+                            C, ff, E, (2 if act == "clamped" else 1) if gated else 0, float(limit), _dt(h), _st()), "moe_up")
+    _check(lib().hyb_moe_down(act_.data_ptr(), idx.data_ptr(), wt.data_ptr() if gated else None, down.data_ptr(),
+                              ypair.data_ptr(), out.data_ptr(), N, top, C, ff, E, h.data_ptr(), _rows(h)[0], _dt(h), _st()),
+           "moe_down")
     return out
 
 
@@ -639,34 +706,41 @@ def gather_scale_rows(h: torch.Tensor, rows: torch.Tensor, scale: Optional[torch
     return out
 
 
-def combine_rows(y: torch.Tensor, where: torch.Tensor, n: int, top: int, wt: Optional[torch.Tensor] = None) -> torch.Tensor:
+def combine_rows(y: torch.Tensor, where: torch.Tensor, n: int, top: int, wt: Optional[torch.Tensor] = None,
+                 idx: Optional[torch.Tensor] = None, n_experts: int = 0, h: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out[t] = sum_k wt[t, k] * y[where[t*top + k]]`` summed in fp32 in the order of ``k`` (int32 ``where``, fp32
-    ``wt [n, top]``; without it a plain sum)."""
+    ``wt [n, top]``; without it a plain sum).  With ``idx [n, top]`` (int32), a choice whose index is ``n_experts`` or more
+    is an identity expert: its term is ``wt[t, k] * h[t]`` and its row of ``y`` is not read."""
     if not y.is_cuda:
         g = y[where.long()].float().view(n, top, -1)
+        if idx is not None:
+            g = torch.where((idx.view(n, top, 1) >= n_experts), h.float().view(n, 1, -1), g)
         if wt is not None:
             g = g * wt.float().view(n, top, 1)
         return g.sum(1).to(y.dtype)
     assert y.is_contiguous() and (wt is None or (wt.is_contiguous() and wt.dtype == torch.float32))
     out = torch.empty(n, y.size(1), device=y.device, dtype=y.dtype)
     _check(lib().hyb_combine_rows(y.data_ptr(), where.data_ptr(), None if wt is None else wt.data_ptr(), out.data_ptr(), n,
-                                  top, y.size(1), _dt(y), _st()), "combine_rows")
+                                  top, y.size(1), None if idx is None else idx.data_ptr(), int(n_experts),
+                                  None if idx is None else h.data_ptr(), 0 if idx is None else _rows(h)[0], _dt(y), _st()),
+           "combine_rows")
     return out
 
 
-_ACTS = {"silu": 0, "gelu_tanh": 1}
+_ACTS = {"silu": 0, "gelu_tanh": 1, "clamped": 2}
 
 
-def act_mul(gu: torch.Tensor, act: str = "silu") -> torch.Tensor:
+def act_mul(gu: torch.Tensor, act: str = "silu", limit: float = 0.0) -> torch.Tensor:
     """``act(gu[:, :F]) * gu[:, F:]`` for rows ``gu [M, 2F]`` (a gated feed-forward whose gate and up projections are
-    one matrix product), evaluated in fp32, result in the activation type."""
+    one matrix product), evaluated in fp32, result in the activation type; ``act="clamped"`` is the clamped product of
+    :func:`glu` with ``limit``."""
     M, F2 = gu.shape
     Fh = F2 // 2
     if not gu.is_cuda:
-        g, u = gu[:, :Fh].float(), gu[:, Fh:].float()
-        return ((F.silu(g) if act == "silu" else F.gelu(g, approximate="tanh")) * u).to(gu.dtype)
+        return glu(gu[:, :Fh].float(), gu[:, Fh:].float(), act, limit).to(gu.dtype)
     out = torch.empty(M, Fh, device=gu.device, dtype=gu.dtype)
-    _check(lib().hyb_act_mul_rows(gu.data_ptr(), _rows(gu)[0], out.data_ptr(), M, Fh, _ACTS[act], _dt(gu), _st()), "act_mul")
+    _check(lib().hyb_act_mul_rows(gu.data_ptr(), _rows(gu)[0], out.data_ptr(), M, Fh, _ACTS[act], float(limit), _dt(gu), _st()),
+           "act_mul")
     return out
 
 
@@ -802,3 +876,109 @@ def gated_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch
                                       None if prep is None else prep.data_ptr(), None if bsig is None else bsig.data_ptr(),
                                       None if oraw is None else oraw.data_ptr(), _st()), "gated_recurrence")
     return out
+
+
+# ---------------------------------------------------------------------------------------------------------
+# post-norm blocks: norm over a whole projection, the fixed-decay recurrence, the norm of a gated sum
+# ---------------------------------------------------------------------------------------------------------
+def full_norm_append(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],
+                     cache: Optional[torch.Tensor], plan: BatchPlan, H: int, G: int, D: int, V: int, nrot: int, eps: float,
+                     qw: torch.Tensor, kw: Optional[torch.Tensor]) -> None:
+    """Per token: the query row (all ``H*D`` values at once) is divided by its root mean square (``eps`` inside the
+    root) and multiplied by ``qw [H*D]``, then the first ``nrot`` entries of every head are rotated (entry ``2i`` with
+    ``2i+1``, angle ``pos * inv_freq[i]``) and the row is kept in place; the key row (``G*D`` values, ``kw``) is treated
+    the same way and written with the values behind it to ``cache[slot, pos]``.  ``k is None``: a layer that reads
+    another layer's keys and values prepares its queries only.  fp32 arithmetic, one rounding at the end."""
+    if not q.is_cuda:
+        N = q.size(0)
+
+        def prep(x: torch.Tensor, heads: int, w: torch.Tensor) -> torch.Tensor:
+            xf = _norm_torch(x, w, None, eps, "rms").reshape(N, heads, D).clone()
+            if nrot:
+                ang = plan.positions.float()[:, None] * inv_freq[None, :]
+                c, s_ = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+                u, w_ = xf[..., 0:nrot:2].clone(), xf[..., 1:nrot:2].clone()
+                xf[..., 0:nrot:2] = u * c - w_ * s_
+                xf[..., 1:nrot:2] = w_ * c + u * s_
+            return xf.reshape(N, heads * D).to(x.dtype)
+
+        q.copy_(prep(q, H, qw))
+        if k is not None:
+            kk = prep(k, G, kw)
+            for r0, n, slot, p0 in plan.seqs:
+                cache[slot, p0:p0 + n, :G * D] = kk[r0:r0 + n]
+                cache[slot, p0:p0 + n, G * D:] = v[r0:r0 + n]
+        return
+    for w in (qw, kw):
+        if w is not None and (w.dtype != q.dtype or not w.is_contiguous()):
+            raise HybridOpsError("norm weights have the activation type")
+    _check(lib().hyb_full_norm_append(q.data_ptr(), _rows(q)[0], None if k is None else k.data_ptr(),
+                                      0 if k is None else _rows(k)[0], None if k is None else v.data_ptr(),
+                                      0 if k is None else _rows(v)[0], None if inv_freq is None else inv_freq.data_ptr(),
+                                      None if k is None else cache.data_ptr(), 0 if k is None else cache.stride(0),
+                                      plan.meta.data_ptr(), plan.tok_seq.data_ptr(), q.size(0), H, G, D, V, int(nrot),
+                                      float(eps), qw.data_ptr(), None if kw is None else kw.data_ptr(), _dt(q), _st()),
+           "full_norm_append")
+
+
+lightning_chunk_from = 16  # a step whose longest sequence brings at least this many tokens takes the chunked kernel
+
+
+def lightning_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
+                         plan: BatchPlan, heads: int, dim: int, vdim: int, variant: int = 0) -> torch.Tensor:
+    """``S <- decay_h S + k v^T``, ``o = S^T q`` per head and token, ``S [dim, vdim]`` fp32 in ``state[slot, head]``
+    (read at the start of the step, written back at its end); no scale.  ``decay`` fp32 ``[heads]``.  Returns the raw
+    read-outs as fp32 ``[N, heads * vdim]``.  ``variant`` (CUDA): 1 the token scan, 2 chunks of 64 tokens (a chunk is
+    four small matrix products; only non-negative powers of the decay occur), 0 chooses by the longest sequence."""
+    N = v.size(0)
+    H, D, V = heads, dim, vdim
+    if state.dtype != torch.float32 or decay.dtype != torch.float32:
+        raise HybridOpsError("recurrent state and decays are fp32")
+    if not q.is_cuda:
+        out = torch.empty(N, H * V, dtype=torch.float32)
+        qf, kf, vf = q.float().reshape(N, H, D), k.float().reshape(N, H, D), v.float().reshape(N, H, V)
+        lam = decay.float()[:, None, None]
+        for r0, n, slot, _ in plan.seqs:
+            S = state[slot].clone()
+            for t in range(r0, r0 + n):
+                S = lam * S + kf[t][:, :, None] * vf[t][:, None, :]
+                out[t] = torch.einsum("hdv,hd->hv", S, qf[t]).reshape(-1)
+            state[slot] = S
+        return out
+    if not variant:
+        variant = 2 if max(n for _, n, _, _ in plan.seqs) >= lightning_chunk_from else 1
+    out = torch.empty(N, H * V, device=v.device, dtype=torch.float32)
+    _check(lib().hyb_lightning(q.data_ptr(), _rows(q)[0], k.data_ptr(), _rows(k)[0], v.data_ptr(), _rows(v)[0],
+                               decay.data_ptr(), state.data_ptr(), plan.meta.data_ptr(), out.data_ptr(), len(plan.seqs),
+                               H, D, V, int(variant), _dt(v), _st()), "lightning_recurrence")
+    return out
+
+
+def norm_gate_rows(o: torch.Tensor, w: torch.Tensor, g: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """``o / rms(o) * w * sigmoid(g)`` over whole rows of fp32 ``o [N, n]`` (``eps`` inside the root), in ``out_dtype``."""
+    if not o.is_cuda:
+        return (_norm_torch(o, w, None, eps, "rms") * torch.sigmoid(g.float())).to(out_dtype)
+    if o.dtype != torch.float32 or not o.is_contiguous() or w.dtype != out_dtype or g.dtype != out_dtype:
+        raise HybridOpsError("read-outs are dense fp32; weight and gate have the activation type")
+    out = torch.empty(o.shape, device=o.device, dtype=out_dtype)
+    _check(lib().hyb_norm_gate_rows(o.data_ptr(), w.data_ptr(), g.data_ptr(), _rows(g)[0], out.data_ptr(), o.size(0), o.size(1),
+                                    float(eps), _dt(out), _st()), "norm_gate_rows")
+    return out
+
+
+def gated_sum_norm_accumulate(resid: torch.Tensor, a: torch.Tensor, b: Optional[torch.Tensor], sg: Optional[torch.Tensor],
+                              w: torch.Tensor, eps: float, kind: str = "rms") -> None:
+    """``resid += norm(a + sigmoid(sg) * b) * w`` in one pass over the fp32 residual: ``a`` and ``b`` are two branches
+    of a feed-forward, ``sg [N, 1]`` one gate logit per token for ``b`` (absent: 1).  All sums are fp32."""
+    if resid.dtype != torch.float32:
+        raise HybridOpsError("the residual stream is fp32")
+    if b is None:
+        return norm_accumulate(resid, a, w, None, eps, kind)
+    if not a.is_cuda:
+        y = a.float() + (torch.sigmoid(sg.float()) if sg is not None else 1.0) * b.float()
+        resid.add_(_norm_torch(y, w, None, eps, kind))
+        return
+    _check(lib().hyb_gated_sum_norm(a.data_ptr(), _rows(a)[0], b.data_ptr(), _rows(b)[0],
+                                    None if sg is None else sg.data_ptr(), 0 if sg is None else sg.stride(0), w.data_ptr(),
+                                    resid.data_ptr(), resid.stride(0), a.size(0), a.size(1), float(eps),
+                                    _NORM_KINDS[kind], _dt(a), _st()), "gated_sum_norm")
