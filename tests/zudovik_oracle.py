@@ -65,16 +65,16 @@ def attention_mixer(W: Dict[str, torch.Tensor], pre: str, m: Dict[str, Any], h: 
     H, G = m["heads"], m["kv_heads"]
     q = attention_queries(W, pre, m, h, t, eps)
     gate = sigmoid(W[pre + "g"] @ h)
+    K, Vv = torch.stack(keys[:t + 1]), torch.stack(values[:t + 1])  # [t+1, G, .]
     outs = []
     for a in range(H):
         g = a // (H // G)
-        s = torch.stack([(q[a] * keys[j][g]).sum() for j in range(t + 1)]) * m["scale"]
+        s = (K[:, g] @ q[a]) * m["scale"]  # one score per position j <= t
         cap = m.get("softcap", 0.0)
         if cap:
             s = cap * torch.tanh(s / cap)
         p = sink_softmax(s, W[pre + "sink"][a])
-        o = sum(p[j] * values[j][g] for j in range(t + 1))
-        outs.append(o * gate[a])
+        outs.append((p @ Vv[:, g]) * gate[a])
     return W[pre + "o"] @ torch.cat(outs)
 
 
@@ -162,3 +162,52 @@ def forward(cfg: Dict[str, Any], W: Dict[str, torch.Tensor], tokens: List[int], 
     if layers_out is not None:
         layers_out.append(torch.stack([torch.stack(rows) for rows in per_layer]))
     return torch.stack(logits)
+
+
+def random_tensors(cfg: Dict[str, Any], seed: int = 0) -> Dict[str, torch.Tensor]:
+    """Weights by checkpoint name for ``cfg``, rounded to bfloat16 values (kept in float32)."""
+    g = torch.Generator().manual_seed(seed)
+    C = cfg["width"]
+
+    def mat(o: int, i: int, gain: float = 1.0) -> torch.Tensor:
+        return torch.randn(o, i, generator=g) * gain / math.sqrt(i)
+
+    def vec(n: int, mean: float = 0.0, std: float = 0.3) -> torch.Tensor:
+        return mean + torch.randn(n, generator=g) * std
+
+    W = {"embed": torch.randn(cfg["vocab"], C, generator=g), "head": mat(cfg["vocab"], C), "final.norm": vec(C, 1.0, 0.1)}
+
+    def expert(pre: str, ff: int) -> None:
+        W[pre + "gate"], W[pre + "up"], W[pre + "down"] = mat(ff, C, 2.0), mat(ff, C, 2.0), mat(C, ff)
+
+    for i, spec in enumerate(cfg["layers"]):
+        m, pre = spec["mixer"], f"l{i}.mix."
+        W[f"l{i}.norm1"] = vec(C, 1.0, 0.1)
+        if spec["type"] == "lightning":
+            H, D, V = m["heads"], m["dim"], m["vdim"]
+            W[pre + "q"], W[pre + "k"], W[pre + "v"], W[pre + "g"] = mat(H * D, C), mat(H * D, C), mat(H * V, C), mat(H * V, C)
+            W[pre + "o"], W[pre + "norm"] = mat(C, H * V), vec(H * V, 1.0, 0.1)
+        else:
+            H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            W[pre + "q"], W[pre + "q.b"], W[pre + "q.norm"] = mat(H * D, C), vec(H * D), vec(H * D, 1.0, 0.2)
+            if m.get("kv_from") is None:
+                W[pre + "k"], W[pre + "k.b"], W[pre + "k.norm"] = mat(G * D, C), vec(G * D), vec(G * D, 1.0, 0.2)
+                W[pre + "v"], W[pre + "v.b"] = mat(G * V, C), vec(G * V)
+            W[pre + "sink"], W[pre + "g"], W[pre + "o"] = vec(H, 0.0, 1.0), mat(H, C), mat(C, H * V)
+        mlp = spec.get("mlp")
+        if not mlp:
+            continue
+        W[f"l{i}.norm2"] = vec(C, 1.0, 0.1)
+        pre = f"l{i}.mlp."
+        if mlp["kind"] == "dense":
+            W[pre + "up"], W[pre + "down"] = mat(mlp["ff"], C), mat(C, mlp["ff"])
+            continue
+        r = mlp["router"]
+        n_out = r["experts"] + r.get("identity", 0)
+        W[pre + "router"], W[pre + "correction"] = mat(n_out, C, 2.0), vec(n_out, 0.0, 0.05)
+        for e in range(r["experts"]):
+            expert(f"{pre}e{e}.", mlp["expert"]["ff"])
+        if mlp.get("shared"):
+            expert(pre + "shared.", mlp["shared"]["ff"])
+            W[pre + "shared.sg"] = mat(1, C)
+    return {k: v.to(torch.bfloat16).float() for k, v in W.items()}
