@@ -153,10 +153,11 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-table", "reference-nccl"],
                     help="reference = byte-stock reference; reference-table = + injected partition-table entry for node counts it lacks; "
                          "reference-nccl = its data plane swapped for torch.distributed send/recv (baseline/nccl_connections.py)")
-    ap.add_argument("--family", default="", choices=["", "hybrid", "vudelix", "labepel"],
+    ap.add_argument("--family", default="", choices=["", "hybrid", "vudelix", "labepel", "zudovik"],
                     help="side benchmark: prefill/decode of the hybrid model family beside a transformer of the same size, or "
                          "(vudelix) of its pre-norm design beside its sandwich design of the same width, or (labepel) of its "
-                         "parallel-block design beside the pre-norm design of the same width "
+                         "parallel-block design beside the pre-norm design of the same width, or (zudovik) of its post-norm "
+                         "design beside the parallel-block design of the same width "
                          "(prints its own JSON line; the default workload is untouched)")
     ap.add_argument("--family-widths", default="1024,2048,4096")
     ap.add_argument("--model", default="Llama-3-8B")

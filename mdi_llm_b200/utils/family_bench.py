@@ -21,6 +21,12 @@ mixing, softmax-routed gated experts plus a shared expert, layer scale, learned 
 of the same width, whose windowed attention and mixture of experts are the closest existing kernels.  Decoding is
 timed inside one chunk (the prompt ends short of a chunk edge), so that a step sees about as many keys as the
 windowed design does.
+
+``bench.py --family zudovik`` measures the post-norm design (causal grouped-query attention with the norm over the
+whole q and k projections, a score cap and learned sinks, a layer on another layer's keys and values, the fixed-decay
+linear recurrence, clamped gated experts with identity experts and a token-gated shared expert) beside the
+parallel-block design of the same width, whose attention and mixture of experts are the closest existing kernels; the
+recurrence is set beside the gated linear attention of the sandwich design, timed in the same run.
 """
 from __future__ import annotations
 
@@ -30,7 +36,24 @@ from typing import Any, Callable, Dict, List
 
 import torch
 
-__all__ = ["run_family_compare", "hybrid_bench_config", "vudelix_bench_config", "labepel_bench_config"]
+__all__ = ["run_family_compare", "hybrid_bench_config", "vudelix_bench_config", "labepel_bench_config", "zudovik_bench_config"]
+
+
+def zudovik_bench_config(width: int) -> Dict[str, Any]:
+    """4 layers: attention + dense (squared ReLU, ``4 * width``), recurrence + experts, attention + experts, attention on
+    the third layer's keys and values + experts.  Two of eight clamped experts of width ``width`` plus two identity
+    outputs in the router, and a token-gated shared expert of width ``width`` (the parallel-block design's expert sizes)."""
+    h = width // 128
+    att = {"heads": h, "kv_heads": max(1, h // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
+           "rot": {"dims": 64, "base": 250000.0}}
+    lit = {"heads": h, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-3 - 5 * i / max(1, h - 1)) for i in range(h)]}
+    moe = {"kind": "moe", "expert": {"ff": width, "limit": 7.0}, "router": {"experts": 8, "identity": 2, "top": 2},
+           "shared": {"ff": width, "limit": 7.0}}
+    layers = [{"type": "attention", "mixer": dict(att), "mlp": {"kind": "dense", "ff": 4 * width}},
+              {"type": "lightning", "mixer": lit, "mlp": dict(moe)}, {"type": "attention", "mixer": dict(att), "mlp": dict(moe)},
+              {"type": "attention", "mixer": {**att, "kv_from": 2}, "mlp": dict(moe)}]
+    return {"architecture": "Zudovik", "vocab": 32000, "width": width, "embedding": {"scale": width ** 0.5}, "layers": layers,
+            "norm": {"eps": 1e-6}}
 
 
 def vudelix_bench_config(width: int, window: int = 1024) -> Dict[str, Any]:
@@ -106,7 +129,8 @@ def _hybrid(width: int, prompt_len: int, batch: int, steps: int, warmup: int, de
     from ..parallel.hybrid_runner import HybridRunner
 
     dev = torch.device("cuda")
-    make = {"hybrid": hybrid_bench_config, "vudelix": vudelix_bench_config, "labepel": labepel_bench_config}[design]
+    make = {"hybrid": hybrid_bench_config, "vudelix": vudelix_bench_config, "labepel": labepel_bench_config,
+            "zudovik": zudovik_bench_config}[design]
     cfg = HybridConfig.from_dict(make(width))
     model = HybridLM(cfg, {}).init_random(dev, torch.bfloat16, seed=1)
     params = sum(p.numel() for p in model.tensor_map().values())
@@ -139,7 +163,8 @@ def _hybrid(width: int, prompt_len: int, batch: int, steps: int, warmup: int, de
         out[f"decode_tok_s_b{b}"] = round(b / ms * 1e3, 1)
         out[f"decode_ms_b{b}"] = round(ms, 4)
         del r
-    kernels = {"hybrid": _hybrid_kernels, "vudelix": _vudelix_kernels, "labepel": _labepel_kernels}[design]
+    kernels = {"hybrid": _hybrid_kernels, "vudelix": _vudelix_kernels, "labepel": _labepel_kernels,
+               "zudovik": _zudovik_kernels}[design]
     out["kernels"] = kernels(model, prompt_len, batch)
     return out
 
@@ -208,6 +233,106 @@ def _vudelix_kernels(model: Any, T: int, batch: int) -> List[Dict[str, Any]]:
         y = torch.randn(N, C, device=dev).to(dt)
         ms = _time(lambda: H.norm_accumulate(x, y, None, None, 1e-6, "none", 0.5), 5, 3, flush)
         rec("scaled_residual_add", phase, ms, N * C * 10.0, 0.0)
+        del pool
+    return rows
+
+
+def _zudovik_kernels(model: Any, T: int, batch: int) -> List[Dict[str, Any]]:
+    """The post-norm design's own kernels alone, on the prompt shape and on the decode shape; ``like`` names the row of
+    ``_labepel_kernels`` (or, for the recurrence, of ``_hybrid_kernels``) that does the corresponding work."""
+    from ..ops import hybrid as H
+
+    pk = _peaks()
+    dev, dt = model.device, model.dtype
+    C = model.config.width
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rows: List[Dict[str, Any]] = []
+
+    def rec(name: str, like: str, phase: str, ms: float, nbytes: float, flops: float) -> None:
+        rows.append({"kernel": name, "like": like, "phase": phase, "ms": round(ms, 4), "gb_s": round(nbytes / ms / 1e6, 1),
+                     "tflops": round(flops / ms / 1e9, 2),
+                     "frac_of_roofline": round(max(nbytes / ms / 1e6 / pk["hbm_gbs"], flops / ms / 1e9 / pk["bf16_tflops"]), 4),
+                     "peaks": pk["source"]})
+
+    att, lit, moe, dense = model.blocks[2].mix, model.blocks[1].mix, model.blocks[2].mlp, model.blocks[0].mlp
+    Hh, G, D, V = att.H, att.G, att.D, att.V
+    for phase, lengths, starts in (("prefill", [T], [0]), ("decode", [1] * batch, [T] * batch)):
+        n_seq, N = len(lengths), sum(lengths)
+        pool = model.new_pool(n_seq, T + 8)
+        plan = H.BatchPlan.make(lengths, list(range(n_seq)), starts, dev)
+        cache = pool.runs[2]["cache"]
+        cache.normal_()
+        tok = torch.randint(0, model.config.vocab, (N,), device=dev, dtype=torch.int32)
+        ms = _time(lambda: H.embed_rows(model.embed, tok, None, plan, model.config.embed_scale), 5, 3, flush)
+        rec("embed_rows[scale]", "embed_rows[positions]", phase, ms, N * C * 6.0, 0.0)
+        x = torch.randn(N, C, device=dev)
+        ms = _time(lambda: model.blocks[0]._read(x, dt), 5, 3, flush)
+        rec("cast_rows", "", phase, ms, N * C * 6.0, 0.0)
+        h = torch.randn(N, C, device=dev).to(dt)
+        p = H.linear(h, att.w_in, att.b_in)
+        q, g = att.col(p, "q"), att.col(p, "g")
+        pairs = sum(s + i + 1 for n, s in zip(lengths, starts) for i in range(n))
+        ms = _time(lambda: H.full_norm_append(q, att.col(p, "k"), att.col(p, "v"), att.inv_freq, cache, plan, Hh, G, D, V, att.nrot,
+                                              1e-6, att.q_norm, att.k_norm), 5, 3, flush)
+        rec("full_norm_append", "window_append[weights, value mixing]", phase, ms, 2.0 * N * (2 * Hh * D + 2 * G * (D + V)), 0.0)
+        if phase == "prefill":
+            ms = _time(lambda: H.head_gate(att._banded(q, cache, plan), g), 5, 3, flush)
+            rec("causal_attn(gemm+softmax)", "chunk_attn(gemm+softmax)", phase, ms, 2.0 * N * (Hh * (D + 2 * V) + G * (D + V)),
+                2.0 * Hh * pairs * (D + V))
+            nb = min(N, att.query_block)
+            s32 = torch.randn(Hh, nb, N, device=dev)
+            ms = _time(lambda: H.causal_softmax(s32, N - nb, att.scale, dt, sink=True, split=True, cap=att.softcap,
+                                                sink_vals=att.sink32), 5, 3, flush)
+            rec("causal_softmax[cap, learned sink, split weights]", "causal_softmax[sink, split weights]", phase, ms,
+                s32.numel() * 8.0, 0.0)
+            del s32
+        else:
+            ms = _time(lambda: H.window_attn(q, g, cache, plan, Hh, G, D, V, att.scale, 0, sink=True, cap=att.softcap,
+                                             sink_vals=att.sink32), 5, 3, flush)
+            keys = sum(s + 1 for s in starts)
+            rec("window_attn[causal, cap, learned sink]", "window_attn[chunk, sink, channel gate]", phase, ms,
+                2.0 * G * keys * (D + V) + 2.0 * N * Hh * (D + V), 2.0 * Hh * pairs * (D + V))
+        # the recurrent mixer
+        LH, LD, LV = lit.H, lit.D, lit.V
+        pl = H.linear(h, lit.w_in)
+        ms = _time(lambda: H.silu_rows(pl[:, :2 * LH * LD + LH * LV]), 5, 3, flush)
+        rec("silu_rows", "act_mul", phase, ms, 4.0 * N * (2 * LH * LD + LH * LV), 0.0)
+        a = H.silu_rows(pl[:, :2 * LH * LD + LH * LV])
+        state = pool.runs[1]["state"]
+        ms = _time(lambda: H.lightning_recurrence(a[:, :LH * LD], a[:, LH * LD:2 * LH * LD], a[:, 2 * LH * LD:], lit.decay, state,
+                                                  plan, LH, LD, LV), 5, 3, flush)
+        nbytes = 2.0 * N * (2 * LH * LD + LH * LV) + 4.0 * N * LH * LV + 8.0 * n_seq * LH * LD * LV
+        rec("lightning_recurrence[chunks]" if phase == "prefill" else "lightning_recurrence[scan]", "gated_recurrence[gla]", phase,
+            ms, nbytes, 4.0 * N * LH * LD * LV)
+        o = torch.randn(N, LH * LV, device=dev)
+        ms = _time(lambda: H.norm_gate_rows(o, lit.norm, lit.col(pl, "g"), 1e-6, dt), 5, 3, flush)
+        rec("norm_gate_rows", "rms_norm[1 + w]", phase, ms, N * LH * LV * 8.0, 0.0)
+        # feed-forwards
+        z = H.linear_f32(h, moe.router32)
+        ms = _time(lambda: H.router_topk(z, moe.top, "softmax_all", moe.correction32), 5, 3, flush)
+        rec("router_topk[softmax over all, correction]", "router_topk[softmax]", phase, ms, 4.0 * N * (moe.E + moe.identity + 2 * moe.top), 0.0)
+        ms = _time(lambda: moe(h), 5, 3, flush)
+        wbytes = 2.0 * 3 * C * moe.ff * min(moe.E, N * moe.top)
+        form = "index-driven" if N * moe.top <= moe.gemv_max else "grouped gemm"
+        rec(f"moe_experts[{form}, clamped, identity]", f"moe_experts[{form}, gated]", phase, ms, wbytes + 2.0 * N * C * (1 + moe.top),
+            6.0 * N * moe.top * C * moe.ff)
+        sh = moe.shared
+        ms = _time(lambda: sh.gated(h), 5, 3, flush)
+        rec("shared_expert(gemm+clamped product)", "shared_expert(gemm+silu*up)", phase, ms, 2.0 * 3 * C * sh.ff + 4.0 * N * C,
+            6.0 * N * C * sh.ff)
+        gu = H.linear(h, sh.w_in)
+        ms = _time(lambda: H.act_mul(gu[:, :2 * sh.ff], "clamped", sh.limit), 5, 3, flush)
+        rec("act_mul[clamped]", "act_mul", phase, ms, 2.0 * N * 3 * sh.ff, 0.0)
+        ms = _time(lambda: dense(h), 5, 3, flush)
+        rec("dense_ff(gemm+relu2)", "shared_expert(gemm+silu*up)", phase, ms, 2.0 * 2 * C * dense.up.size(0) + 4.0 * N * C,
+            4.0 * N * C * dense.up.size(0))
+        ya, yb = (torch.randn(N, C, device=dev).to(dt) for _ in range(2))
+        sg = torch.randn(N, 1, device=dev).to(dt)
+        blk = model.blocks[2]
+        ms = _time(lambda: H.norm_accumulate(x, ya, blk.norm1.w, None, 1e-6, "rms"), 5, 3, flush)
+        rec("post_norm_accumulate", "scaled_branches", phase, ms, N * C * 10.0, 0.0)
+        ms = _time(lambda: H.gated_sum_norm_accumulate(x, ya, yb, sg, blk.norm2.w, 1e-6), 5, 3, flush)
+        rec("gated_sum_norm_accumulate", "scaled_branches", phase, ms, N * C * 12.0, 0.0)
         del pool
     return rows
 
@@ -430,6 +555,28 @@ def run_family_compare(widths: List[int], prompt_len: int = 2048, batch: int = 8
             torch.cuda.empty_cache()
             results.append({"width": w, "vudelix": new, "hybrid": old})
         return {"metric": "family_compare", "family": "vudelix", "dtype": "bf16", "data": "synthetic", "prompt_len": prompt_len,
+                "decode_batch": batch, "steps": steps, "warmup": warmup, "l2": "flushed between single-kernel timings",
+                "results": results}
+    if family == "zudovik":
+        from ..models.config import HybridConfig
+        from ..models.hybrid import HybridLM
+
+        for w in widths:
+            new = _hybrid(w, prompt_len, batch, steps, warmup, "zudovik")
+            torch.cuda.empty_cache()
+            old = _hybrid(w, prompt_len, batch, steps, warmup, "labepel")
+            torch.cuda.empty_cache()
+            # the recurrence's like kernel lives in the sandwich design: its kernels alone, no model-level timing
+            sandwich = HybridLM(HybridConfig.from_dict(hybrid_bench_config(w)), {}).init_random(torch.device("cuda"), torch.bfloat16, seed=1)
+            rec_rows = [k for k in _hybrid_kernels(sandwich, prompt_len, batch) if k["kernel"] == "gated_recurrence[gla]"]
+            del sandwich
+            torch.cuda.empty_cache()
+            theirs = {(k["kernel"], k["phase"]): k["frac_of_roofline"] for k in old["kernels"] + rec_rows}
+            for k in new["kernels"]:  # how far from its roofline, relative to the like kernel (above 1: this one is nearer)
+                other = theirs.get((k["like"], k["phase"]))
+                k["roofline_vs_like"] = round(k["frac_of_roofline"] / other, 3) if other else None
+            results.append({"width": w, "zudovik": new, "labepel": old, "sandwich_recurrence": rec_rows})
+        return {"metric": "family_compare", "family": "zudovik", "dtype": "bf16", "data": "synthetic", "prompt_len": prompt_len,
                 "decode_batch": batch, "steps": steps, "warmup": warmup, "l2": "flushed between single-kernel timings",
                 "results": results}
     if family == "labepel":
