@@ -729,8 +729,8 @@ class LightningAttention(nn.Module, _Fused):
     """Linear attention with one fixed decay per head: ``q, k, v = silu(W h)``, ``S_t = decay_h S_(t-1) + k_t v_t^T``
     (fp32, one ``[dim, vdim]`` matrix per head and slot, zero for a fresh slot), ``o_t = S_t^T q_t`` without a scale; the
     heads' read-outs, side by side, get ONE RMS norm with the weight ``norm [heads * vdim]``, are multiplied by
-    ``sigmoid(W_g h)`` and projected by ``W_o``.  q, k, v and the gate are one matrix product; the SiLU of q, k, v is one
-    pass over their columns."""
+    ``sigmoid(W_g h)`` and projected by ``W_o``.  q, k, v and the gate are one matrix product; the SiLU of q, k, v is
+    taken inside the recurrence kernels, where they are read."""
 
     tensor_names = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "norm": "norm"}
 
@@ -749,15 +749,17 @@ class LightningAttention(nn.Module, _Fused):
     def forward(self, h: torch.Tensor, plan: H.BatchPlan, st: Dict[str, torch.Tensor]) -> torch.Tensor:
         HD, HV = self.H * self.D, self.H * self.V
         p = H.linear(h, self.w_in)
-        a = H.silu_rows(p[:, :2 * HD + HV])
-        o = H.lightning_recurrence(a[:, :HD], a[:, HD:2 * HD], a[:, 2 * HD:], self.decay, st["state"], plan, self.H, self.D, self.V)
+        o = H.lightning_recurrence(self.col(p, "q"), self.col(p, "k"), self.col(p, "v"), self.decay, st["state"], plan,
+                                   self.H, self.D, self.V, act=True)
         return H.linear(H.norm_gate_rows(o, self.norm, self.col(p, "g"), self.eps, h.dtype), self.o)
 
 
 class PostNormBlock(nn.Module):
     """``x += norm1(mixer(x))``, then ``x += norm2(ff(x))`` when the layer has a feed-forward: the sublayers read the
     residual stream itself (rounded to the activation type), only their outputs are normed.  A mixture of experts with
-    a shared expert adds ``sigmoid(sg) * shared(x)`` to the routed sum inside the same norm."""
+    a shared expert adds ``sigmoid(sg) * shared(x)`` to the routed sum inside the same norm.  With 16-bit activations
+    the kernel that adds a sublayer's normed output to the residual also writes the rounded copy the next sublayer
+    reads (handed from block to block through the step's scratch), so the stream is not read again for a cast."""
 
     side = None
 
@@ -774,26 +776,36 @@ class PostNormBlock(nn.Module):
         return ["norm1"] + (["norm2"] if self.mlp is not None else [])
 
     @staticmethod
-    def _read(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    def _read(x: torch.Tensor, dtype: torch.dtype, plan: Optional[H.BatchPlan] = None) -> torch.Tensor:
+        """The stream as a sublayer reads it: itself in fp32, else the rounded copy the last update left, else a cast."""
         if dtype == torch.float32:
             return x
-        h = torch.empty(x.shape, device=x.device, dtype=dtype)
-        H.cast_into(x, h)
+        h = plan.shared.pop("stream_copy", None) if plan is not None else None
+        if h is None:
+            h = torch.empty(x.shape, device=x.device, dtype=dtype)
+            H.cast_into(x, h)
         return h
 
     def forward(self, x: torch.Tensor, plan: H.BatchPlan, st: Dict[str, torch.Tensor], dtype: torch.dtype,
                 tokens: Optional[torch.Tensor] = None, side_table: Optional[torch.Tensor] = None) -> None:
-        H.norm_accumulate(x, self.mix(self._read(x, dtype), plan, st), self.norm1.w, None, self.eps, self.kind)
+        h = self._read(x, dtype, plan)
+        nxt = None if dtype == torch.float32 else torch.empty(x.shape, device=x.device, dtype=dtype)
+        H.norm_accumulate(x, self.mix(h, plan, st), self.norm1.w, None, self.eps, self.kind, copy=nxt)
+        if nxt is not None:
+            plan.shared["stream_copy"] = nxt
         if self.mlp is None:
             return
-        h = self._read(x, dtype)
+        h = self._read(x, dtype, plan)
+        nxt = None if dtype == torch.float32 else torch.empty(x.shape, device=x.device, dtype=dtype)
         y = self.mlp(h)
         shared = getattr(self.mlp, "shared", None)
         if shared is None:
-            H.norm_accumulate(x, y, self.norm2.w, None, self.eps, self.kind)
-            return
-        y2, sg = shared.gated(h)
-        H.gated_sum_norm_accumulate(x, y, y2, sg, self.norm2.w, self.eps, self.kind)
+            H.norm_accumulate(x, y, self.norm2.w, None, self.eps, self.kind, copy=nxt)
+        else:
+            y2, sg = shared.gated(h)
+            H.gated_sum_norm_accumulate(x, y, y2, sg, self.norm2.w, self.eps, self.kind, copy=nxt)
+        if nxt is not None:
+            plan.shared["stream_copy"] = nxt
 
 
 class ParallelBlock(nn.Module):
@@ -1021,6 +1033,7 @@ class HybridLM(nn.Module):
         x = x0.clone() if self.loop_in is not None else x0
         for run, (li, first) in enumerate(self.runs):
             if first:
+                plan.shared.pop("stream_copy", None)  # the stream is about to change outside a block
                 cat = torch.empty(x.size(0), 2 * C, device=x.device, dtype=dt)
                 H.cast_into(x, cat[:, :C])
                 H.cast_into(x0, cat[:, C:])

@@ -110,10 +110,12 @@ __global__ void cast_rows_kernel(const Tin* __restrict__ in, long long in_stride
 // kind 0: (x - mean) / sqrt(var + eps) * w + b      kind 1: x / sqrt(mean(x^2) + eps) * w
 // kind 2: x (no normalisation).  accumulate != 0: out (fp32) += scale * result, the residual update of a block;
 // else out = result.  The weight applied is w_offset + w (w_offset = 1: a weight stored as its deviation from one).
+// copy (optional, dense rows of n, with accumulate): the updated residual rounded to the weight's type, which is what
+// the next sublayer of a post-norm block reads.
 template <typename Tin, typename Tw, typename Tout>
 __global__ void norm_rows_kernel(const Tin* __restrict__ in, long long in_stride, const Tw* __restrict__ w,
                                  const Tw* __restrict__ b, Tout* __restrict__ out, long long out_stride, int n,
-                                 float eps, int kind, int accumulate, float scale, float w_offset) {
+                                 float eps, int kind, int accumulate, float scale, float w_offset, Tw* __restrict__ copy) {
   __shared__ float red[33];
   const Tin* src = in + (size_t)blockIdx.x * in_stride;
   Tout* dst = out + (size_t)blockIdx.x * out_stride;
@@ -141,8 +143,13 @@ __global__ void norm_rows_kernel(const Tin* __restrict__ in, long long in_stride
     float y = (to_f(src[i]) - mean) * inv;
     if (w) y *= w_offset + to_f(w[i]);
     if (b) y += to_f(b[i]);
-    if (accumulate) dst[i] = from_f<Tout>(to_f(dst[i]) + scale * y);
-    else dst[i] = from_f<Tout>(y);
+    if (accumulate) {
+      float r = to_f(dst[i]) + scale * y;
+      dst[i] = from_f<Tout>(r);
+      if (copy) copy[(size_t)blockIdx.x * n + i] = from_f<Tw>(r);
+    } else {
+      dst[i] = from_f<Tout>(y);
+    }
   }
 }
 
@@ -871,11 +878,12 @@ int hyb_cast_rows(const void* in, long long in_stride, int in_dt, void* out, lon
 // {bf16, fp32}.
 int hyb_norm_rows(const void* in, long long in_stride, int in_dt, const void* w, const void* b, int w_dt, void* out,
                   long long out_stride, int out_dt, int rows, int n, float eps, int kind, int accumulate, float scale,
-                  float w_offset, cudaStream_t st) {
+                  float w_offset, void* copy, cudaStream_t st) {
   if (rows == 0) return 0;
+  if (copy && (!accumulate || kind == 2)) return -2;
 #define NR(TI, TW, TO)                                                                                              \
   norm_rows_kernel<TI, TW, TO><<<rows, 256, 0, st>>>((const TI*)in, in_stride, (const TW*)w, (const TW*)b, (TO*)out, \
-                                                      out_stride, n, eps, kind, accumulate, scale, w_offset)
+                                                      out_stride, n, eps, kind, accumulate, scale, w_offset, (TW*)copy)
   if (w_dt == 1) {
     if (in_dt != 1 || out_dt != 1) return -3;
     NR(float, float, float);
@@ -2066,14 +2074,16 @@ __global__ void full_norm_append_kernel(T* __restrict__ q, long long q_stride, c
 // Grid (sequence, head, 32-column tile of V); thread (lane, dg) keeps S[dg + 8 i][v0 + lane] in registers (D <= 256),
 // the eight row groups' partial read-outs meet in shared memory.  The form for one-token steps and short portions;
 // o is written raw (fp32 [N, H * V]): the norm over all heads and the gate follow in norm_gate_rows_kernel.
+// act != 0: q, k and v are pre-activations and their SiLU is taken (in fp32) where they are loaded.
 #define LS_MAXI 32
+__device__ __forceinline__ float lin_act(float x, int act) { return act ? siluf_(x) : x; }
 template <typename T>
 __global__ void __launch_bounds__(256) lightning_scan_kernel(const T* __restrict__ q, long long q_stride,
                                                              const T* __restrict__ k, long long k_stride,
                                                              const T* __restrict__ v, long long v_stride,
                                                              const float* __restrict__ decay, float* __restrict__ state,
                                                              const int* __restrict__ meta, float* __restrict__ oraw,
-                                                             int H, int D, int V) {
+                                                             int H, int D, int V, int act) {
   __shared__ float qs[256], ks[256], part[8][33];
   const int* m = meta + 4 * blockIdx.x;
   int r0 = m[0], n = m[1], slot = m[2];
@@ -2091,10 +2101,10 @@ __global__ void __launch_bounds__(256) lightning_scan_kernel(const T* __restrict
   }
   for (int t = r0; t < r0 + n; ++t) {
     for (int d = threadIdx.x; d < D; d += 256) {
-      qs[d] = to_f(q[(size_t)t * q_stride + (size_t)h * D + d]);
-      ks[d] = to_f(k[(size_t)t * k_stride + (size_t)h * D + d]);
+      qs[d] = lin_act(to_f(q[(size_t)t * q_stride + (size_t)h * D + d]), act);
+      ks[d] = lin_act(to_f(k[(size_t)t * k_stride + (size_t)h * D + d]), act);
     }
-    float vv = live ? to_f(v[(size_t)t * v_stride + (size_t)h * V + vc]) : 0.f;
+    float vv = live ? lin_act(to_f(v[(size_t)t * v_stride + (size_t)h * V + vc]), act) : 0.f;
     __syncthreads();
     float o = 0.f;
 #pragma unroll
@@ -2123,150 +2133,189 @@ __global__ void __launch_bounds__(256) lightning_scan_kernel(const T* __restrict
   }
 }
 
-// The same recurrence over a prompt portion in chunks of LC_L = 64 tokens.  With S the state before the chunk and
-// positions t, s counted inside it,
+// The same recurrence over prompt portions in chunks of LC_L = 64 tokens, parallel over the chunks.  With S the state
+// before a chunk and positions t, s counted inside it,
 //   o_t = lam^(t+1) S^T q_t + sum_{s <= t} lam^(t-s) (q_t . k_s) v_s          S' = lam^len S + sum_s lam^(len-1-s) k_s v_s^T
-// so a chunk is four small matrix products (scores, weighted values, read-out of the old state, state update) instead
-// of 64 dependent steps; powers of lam only have non-negative exponents, so nothing overflows however small lam is.
-// Grid (sequence, head, 32-column tile of V), 256 threads, everything fp32 in shared memory: Q and K of the chunk
-// transposed ([D][68]), the decayed causal scores transposed ([s][t]), the V tile, the state tile [D][32].
-// The scores are recomputed by each column tile of a head; they are a small part of the chunk's arithmetic.
+// so a chunk is four small matrix products instead of 64 dependent steps, and only S' = lam^len S + U chains the chunks
+// of a sequence.  Powers of lam only have non-negative exponents, so nothing overflows however small lam is.  Three
+// kernels over a chunk table ctab[c] = {first token row, tokens, sequence, 0} (chunks of a sequence in order) and
+// stab[seq] = {first chunk, chunks}:
+//   lightning_chunk_state_kernel  grid (chunk, head, 32-column tile of V): U_c = sum_s lam^(len-1-s) k_s v_s^T -> scratch
+//   lightning_chunk_scan_kernel   grid (sequence, head, slices of D*V): walks the sequence's chunks, replaces U_c by the
+//                                 state BEFORE chunk c and leaves the final state in the slot
+//   lightning_chunk_out_kernel    grid (chunk, head, tile of V): decayed causal scores, weighted values, read-out of
+//                                 the state before the chunk
+// Everything is fp32 in shared memory: Q and K of the chunk transposed ([D][68]), the scores transposed ([s][t]), the V
+// tile, the state tile [D][32].  The scores are recomputed by each column tile of a head; they are a small part of a
+// chunk's arithmetic.  scratch is [chunks, H, D, V] fp32.
 #define LC_L 64
 #define LC_LP 68
 #define LC_VT 32
 template <typename T>
-__global__ void __launch_bounds__(256) lightning_chunk_kernel(const T* __restrict__ q, long long q_stride,
-                                                              const T* __restrict__ k, long long k_stride,
-                                                              const T* __restrict__ v, long long v_stride,
-                                                              const float* __restrict__ decay, float* __restrict__ state,
-                                                              const int* __restrict__ meta, float* __restrict__ oraw,
-                                                              int H, int D, int V) {
+__global__ void __launch_bounds__(256) lightning_chunk_state_kernel(const T* __restrict__ k, long long k_stride,
+                                                                    const T* __restrict__ v, long long v_stride,
+                                                                    const float* __restrict__ decay,
+                                                                    const int* __restrict__ ctab, float* __restrict__ scratch,
+                                                                    int H, int D, int V, int act) {
+  extern __shared__ __align__(16) float lsm[];
+  float* Kt = lsm;                       // [D][LC_LP]
+  float* Vs = Kt + (size_t)D * LC_LP;    // [LC_L][LC_VT], already times lam^(len-1-s)
+  float* pw = Vs + LC_L * LC_VT;         // [LC_L + 1]
+  const int* c = ctab + 4 * blockIdx.x;
+  int row0 = c[0], len = c[1];
+  int h = blockIdx.y, v0 = blockIdx.z * LC_VT;
+  int tid = threadIdx.x, lane = tid & 31, tg = tid >> 5;
+  for (int i = tid; i <= LC_L; i += 256) pw[i] = (float)pow((double)decay[h], (double)i);
+  __syncthreads();
+  for (int i = tid; i < LC_L * D; i += 256) {
+    int t = i / D, d = i - t * D;
+    Kt[d * LC_LP + t] = t < len ? lin_act(to_f(k[(size_t)(row0 + t) * k_stride + (size_t)h * D + d]), act) : 0.f;
+  }
+  for (int i = tid; i < LC_L * LC_VT; i += 256) {
+    int t = i >> 5, cc = i & 31;
+    Vs[i] = t < len && v0 + cc < V ? lin_act(to_f(v[(size_t)(row0 + t) * v_stride + (size_t)h * V + v0 + cc]), act) * pw[len - 1 - t] : 0.f;
+  }
+  __syncthreads();
+  float* up = scratch + (((size_t)blockIdx.x * H + h) * D) * V;
+  // thread (lane, tg) owns column lane of rows d = tg + 8 i, four rows at a time
+  for (int i0 = 0; tg + 8 * i0 < D; i0 += 4) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    int dd[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) dd[u] = min(tg + 8 * (i0 + u), D - 1);  // rows past D: computed, not stored
+    for (int s0 = 0; s0 < len; s0 += 4) {  // rows of Kt and Vs are zero past len
+      float w0 = Vs[s0 * LC_VT + lane], w1 = Vs[(s0 + 1) * LC_VT + lane], w2 = Vs[(s0 + 2) * LC_VT + lane],
+            w3 = Vs[(s0 + 3) * LC_VT + lane];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float4 kv = *reinterpret_cast<const float4*>(Kt + dd[u] * LC_LP + s0);
+        acc[u] += kv.x * w0 + kv.y * w1 + kv.z * w2 + kv.w * w3;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      int d = tg + 8 * (i0 + u);
+      if (d < D && v0 + lane < V) up[(size_t)d * V + v0 + lane] = acc[u];
+    }
+  }
+}
+
+__global__ void lightning_chunk_scan_kernel(const float* __restrict__ decay, float* __restrict__ state,
+                                            const int* __restrict__ meta, const int* __restrict__ ctab,
+                                            const int* __restrict__ stab, float* __restrict__ scratch, int H, int D, int V) {
+  int seq = blockIdx.x, h = blockIdx.y;
+  int e = blockIdx.z * blockDim.x + threadIdx.x;  // element of the [D, V] state
+  if (e >= D * V) return;
+  int slot = meta[4 * seq + 2], c0 = stab[2 * seq], nc = stab[2 * seq + 1];
+  double lam = (double)decay[h];
+  float full = (float)pow(lam, (double)LC_L);
+  float* sp = state + (((size_t)slot * H + h) * D) * V + e;
+  float S = *sp;
+  for (int c = c0; c < c0 + nc; ++c) {
+    float* u = scratch + (((size_t)c * H + h) * D) * V + e;
+    int len = ctab[4 * c + 1];
+    float U = *u;
+    *u = S;  // the state before chunk c
+    S = (len == LC_L ? full : (float)pow(lam, (double)len)) * S + U;
+  }
+  *sp = S;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) lightning_chunk_out_kernel(const T* __restrict__ q, long long q_stride,
+                                                                  const T* __restrict__ k, long long k_stride,
+                                                                  const T* __restrict__ v, long long v_stride,
+                                                                  const float* __restrict__ decay,
+                                                                  const int* __restrict__ ctab,
+                                                                  const float* __restrict__ scratch, float* __restrict__ oraw,
+                                                                  int H, int D, int V, int act) {
   extern __shared__ __align__(16) float lsm[];
   float* Qt = lsm;                       // [D][LC_LP]
   float* Kt = Qt + (size_t)D * LC_LP;    // [D][LC_LP]
   float* At = Kt + (size_t)D * LC_LP;    // [LC_L][LC_LP]: At[s][t] = lam^(t-s) q_t . k_s for s <= t, else 0
   float* Vs = At + LC_L * LC_LP;         // [LC_L][LC_VT]
-  float* Ss = Vs + LC_L * LC_VT;         // [D][LC_VT]
+  float* Ss = Vs + LC_L * LC_VT;         // [D][LC_VT]: the state before the chunk
   float* pw = Ss + (size_t)D * LC_VT;    // [LC_L + 1]: lam^i
-  const int* m = meta + 4 * blockIdx.x;
-  int r0 = m[0], n = m[1], slot = m[2];
+  const int* c = ctab + 4 * blockIdx.x;
+  int row0 = c[0], len = c[1];
   int h = blockIdx.y, v0 = blockIdx.z * LC_VT;
   int tid = threadIdx.x, lane = tid & 31, tg = tid >> 5;
   int vc = v0 + lane;
   bool live = vc < V;
-  float* sp = state + (((size_t)slot * H + h) * D) * V;
+  const float* sp = scratch + (((size_t)blockIdx.x * H + h) * D) * V;
   for (int i = tid; i <= LC_L; i += 256) pw[i] = (float)pow((double)decay[h], (double)i);
   for (int i = tid; i < D * LC_VT; i += 256) {
-    int d = i >> 5, c = i & 31;
-    Ss[i] = v0 + c < V ? sp[(size_t)d * V + v0 + c] : 0.f;
+    int d = i >> 5, cc = i & 31;
+    Ss[i] = v0 + cc < V ? sp[(size_t)d * V + v0 + cc] : 0.f;
   }
+  for (int i = tid; i < LC_L * D; i += 256) {
+    int t = i / D, d = i - t * D;
+    size_t row = (size_t)(row0 + t);
+    Qt[d * LC_LP + t] = t < len ? lin_act(to_f(q[row * q_stride + (size_t)h * D + d]), act) : 0.f;
+    Kt[d * LC_LP + t] = t < len ? lin_act(to_f(k[row * k_stride + (size_t)h * D + d]), act) : 0.f;
+  }
+  for (int i = tid; i < LC_L * LC_VT; i += 256) {
+    int t = i >> 5, cc = i & 31;
+    Vs[i] = t < len && v0 + cc < V ? lin_act(to_f(v[(size_t)(row0 + t) * v_stride + (size_t)h * V + v0 + cc]), act) : 0.f;
+  }
+  __syncthreads();
   int ty = tid >> 4, tx = tid & 15;
-  for (int c0 = 0; c0 < n; c0 += LC_L) {
-    int len = min(LC_L, n - c0);
-    __syncthreads();  // the previous chunk is done with every tile; pw and Ss are written
-    for (int i = tid; i < LC_L * D; i += 256) {
-      int t = i / D, d = i - t * D;
-      size_t row = (size_t)(r0 + c0 + t);
-      Qt[d * LC_LP + t] = t < len ? to_f(q[row * q_stride + (size_t)h * D + d]) : 0.f;
-      Kt[d * LC_LP + t] = t < len ? to_f(k[row * k_stride + (size_t)h * D + d]) : 0.f;
-    }
-    for (int i = tid; i < LC_L * LC_VT; i += 256) {
-      int t = i >> 5, c = i & 31;
-      Vs[i] = t < len && v0 + c < V ? to_f(v[(size_t)(r0 + c0 + t) * v_stride + (size_t)h * V + v0 + c]) : 0.f;
-    }
-    __syncthreads();
-    {  // scores: thread (ty, tx) owns t = 4 ty .. 4 ty + 3 against s = 4 tx .. 4 tx + 3
-      float a[4][4];
+  {  // scores: thread (ty, tx) owns t = 4 ty .. 4 ty + 3 against s = 4 tx .. 4 tx + 3
+    float a[4][4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) a[i][j] = 0.f;
-      if (tx <= ty) {  // blocks above the diagonal hold no visible pair
-        for (int d = 0; d < D; ++d) {
-          float4 qv = *reinterpret_cast<const float4*>(Qt + d * LC_LP + 4 * ty);
-          float4 kv = *reinterpret_cast<const float4*>(Kt + d * LC_LP + 4 * tx);
-          const float qa[4] = {qv.x, qv.y, qv.z, qv.w}, ka[4] = {kv.x, kv.y, kv.z, kv.w};
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) a[i][j] += qa[i] * ka[j];
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        int s = 4 * tx + j;
-        float o[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          int t = 4 * ty + i;
-          o[i] = s <= t ? a[i][j] * pw[t - s] : 0.f;
-        }
-        *reinterpret_cast<float4*>(At + s * LC_LP + 4 * ty) = make_float4(o[0], o[1], o[2], o[3]);
-      }
-    }
-    __syncthreads();
-    {  // outputs: thread (lane, tg) owns column v0 + lane of rows t = 8 tg .. 8 tg + 7
-      float in[8], st[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) in[i] = st[i] = 0.f;
-      int smax = min(len, 8 * tg + 8);
-      for (int s = 0; s < smax; ++s) {
-        float vv = Vs[s * LC_VT + lane];
-        float4 a0 = *reinterpret_cast<const float4*>(At + s * LC_LP + 8 * tg);
-        float4 a1 = *reinterpret_cast<const float4*>(At + s * LC_LP + 8 * tg + 4);
-        in[0] += a0.x * vv; in[1] += a0.y * vv; in[2] += a0.z * vv; in[3] += a0.w * vv;
-        in[4] += a1.x * vv; in[5] += a1.y * vv; in[6] += a1.z * vv; in[7] += a1.w * vv;
-      }
+      for (int j = 0; j < 4; ++j) a[i][j] = 0.f;
+    if (tx <= ty) {  // blocks above the diagonal hold no visible pair
       for (int d = 0; d < D; ++d) {
-        float sv = Ss[d * LC_VT + lane];
-        float4 q0 = *reinterpret_cast<const float4*>(Qt + d * LC_LP + 8 * tg);
-        float4 q1 = *reinterpret_cast<const float4*>(Qt + d * LC_LP + 8 * tg + 4);
-        st[0] += q0.x * sv; st[1] += q0.y * sv; st[2] += q0.z * sv; st[3] += q0.w * sv;
-        st[4] += q1.x * sv; st[5] += q1.y * sv; st[6] += q1.z * sv; st[7] += q1.w * sv;
-      }
-      if (live) {
+        float4 qv = *reinterpret_cast<const float4*>(Qt + d * LC_LP + 4 * ty);
+        float4 kv = *reinterpret_cast<const float4*>(Kt + d * LC_LP + 4 * tx);
+        const float qa[4] = {qv.x, qv.y, qv.z, qv.w}, ka[4] = {kv.x, kv.y, kv.z, kv.w};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          int t = 8 * tg + i;
-          if (t < len) oraw[(size_t)(r0 + c0 + t) * H * V + (size_t)h * V + vc] = in[i] + pw[t + 1] * st[i];
-        }
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) a[i][j] += qa[i] * ka[j];
       }
     }
-    __syncthreads();
-    // the values as the state update wants them: v_s lam^(len-1-s)
-    for (int i = tid; i < LC_L * LC_VT; i += 256) {
-      int s = i >> 5;
-      Vs[i] = s < len ? Vs[i] * pw[len - 1 - s] : 0.f;
-    }
-    __syncthreads();
-    {  // state: thread (lane, tg) owns column lane of rows d = tg + 8 i, four rows at a time
-      float lend = pw[len];
-      for (int i0 = 0; tg + 8 * i0 < D; i0 += 4) {
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        int dd[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) dd[u] = min(tg + 8 * (i0 + u), D - 1);  // rows past D: computed, not stored
-        for (int s = 0; s < len; s += 4) {  // rows of Kt are zero past len
-          float w0 = Vs[s * LC_VT + lane], w1 = Vs[(s + 1) * LC_VT + lane], w2 = Vs[(s + 2) * LC_VT + lane],
-                w3 = Vs[(s + 3) * LC_VT + lane];
+    for (int j = 0; j < 4; ++j) {
+      int s_ = 4 * tx + j;
+      float o[4];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            float4 kv = *reinterpret_cast<const float4*>(Kt + dd[u] * LC_LP + s);
-            acc[u] += kv.x * w0 + kv.y * w1 + kv.z * w2 + kv.w * w3;
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          int d = tg + 8 * (i0 + u);
-          if (d < D) Ss[d * LC_VT + lane] = lend * Ss[d * LC_VT + lane] + acc[u];
-        }
+      for (int i = 0; i < 4; ++i) {
+        int t = 4 * ty + i;
+        o[i] = s_ <= t ? a[i][j] * pw[t - s_] : 0.f;
       }
+      *reinterpret_cast<float4*>(At + s_ * LC_LP + 4 * ty) = make_float4(o[0], o[1], o[2], o[3]);
     }
   }
   __syncthreads();
-  for (int i = tid; i < D * LC_VT; i += 256) {
-    int d = i >> 5, c = i & 31;
-    if (v0 + c < V) sp[(size_t)d * V + v0 + c] = Ss[i];
+  {  // outputs: thread (lane, tg) owns column v0 + lane of rows t = 8 tg .. 8 tg + 7
+    float in[8], st[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) in[i] = st[i] = 0.f;
+    int smax = min(len, 8 * tg + 8);
+    for (int s_ = 0; s_ < smax; ++s_) {
+      float vv = Vs[s_ * LC_VT + lane];
+      float4 a0 = *reinterpret_cast<const float4*>(At + s_ * LC_LP + 8 * tg);
+      float4 a1 = *reinterpret_cast<const float4*>(At + s_ * LC_LP + 8 * tg + 4);
+      in[0] += a0.x * vv; in[1] += a0.y * vv; in[2] += a0.z * vv; in[3] += a0.w * vv;
+      in[4] += a1.x * vv; in[5] += a1.y * vv; in[6] += a1.z * vv; in[7] += a1.w * vv;
+    }
+    for (int d = 0; d < D; ++d) {
+      float sv = Ss[d * LC_VT + lane];
+      float4 q0 = *reinterpret_cast<const float4*>(Qt + d * LC_LP + 8 * tg);
+      float4 q1 = *reinterpret_cast<const float4*>(Qt + d * LC_LP + 8 * tg + 4);
+      st[0] += q0.x * sv; st[1] += q0.y * sv; st[2] += q0.z * sv; st[3] += q0.w * sv;
+      st[4] += q1.x * sv; st[5] += q1.y * sv; st[6] += q1.z * sv; st[7] += q1.w * sv;
+    }
+    if (live) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        int t = 8 * tg + i;
+        if (t < len) oraw[(size_t)(row0 + t) * H * V + (size_t)h * V + vc] = in[i] + pw[t + 1] * st[i];
+      }
+    }
   }
 }
 
@@ -2287,12 +2336,13 @@ __global__ void norm_gate_rows_kernel(const float* __restrict__ o, const T* __re
 
 // resid[r] += norm(a[r] + sigmoid(sg[r]) * b[r]) * w: the post-norm of a feed-forward whose always-on branch b is
 // weighed by one sigmoid gate per token, and the residual sum, in one pass (fp32 arithmetic; b and sg optional).
+// copy (optional, dense): the updated residual rounded to the activation type, for the next sublayer to read.
 // kind 0: layer norm without bias, 1: RMS norm.
 template <typename T>
 __global__ void gated_sum_norm_kernel(const T* __restrict__ a, long long a_stride, const T* __restrict__ b,
                                       long long b_stride, const T* __restrict__ sg, long long sg_stride,
                                       const T* __restrict__ w, float* __restrict__ resid, long long r_stride, int n,
-                                      float eps, int kind) {
+                                      float eps, int kind, T* __restrict__ copy) {
   __shared__ float red[33];
   size_t r = blockIdx.x;
   float gt = b ? (sg ? sigmoidf_(to_f(sg[r * sg_stride])) : 1.f) : 0.f;
@@ -2310,7 +2360,9 @@ __global__ void gated_sum_norm_kernel(const T* __restrict__ a, long long a_strid
   float inv = 1.f / sqrtf(block_sum(ss, red) / n + eps);
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     float y = to_f(a[r * a_stride + i]) + (b ? gt * to_f(b[r * b_stride + i]) : 0.f) - mean;
-    resid[r * r_stride + i] += y * inv * to_f(w[i]);
+    float x = resid[r * r_stride + i] + y * inv * to_f(w[i]);
+    resid[r * r_stride + i] = x;
+    if (copy) copy[r * n + i] = from_f<T>(x);
   }
 }
 
@@ -2335,33 +2387,47 @@ int hyb_full_norm_append(void* q, long long q_stride, const void* k, long long k
   return (int)cudaGetLastError();
 }
 
-// variant 1: token scan; 2: chunks of 64 tokens.  decay [H] fp32 on the device; oraw [N, H * V] fp32.
+// variant 1: token scan; 2: chunks of 64 tokens (ctab [nchunks, 4], stab [nseq, 2] int32 and scratch
+// [nchunks, H, D, V] fp32 on the device, see the kernels).  decay [H] fp32 on the device; oraw [N, H * V] fp32.
+// act != 0: q, k, v are pre-activations; their SiLU is taken on load.
 int hyb_lightning(const void* q, long long q_stride, const void* k, long long k_stride, const void* v, long long v_stride,
                   const float* decay, float* state, const int* meta, float* oraw, int nseq, int H, int D, int V,
-                  int variant, int dt, cudaStream_t st) {
+                  int variant, int act, const int* ctab, const int* stab, int nchunks, float* scratch, int dt,
+                  cudaStream_t st) {
   if (nseq == 0) return 0;
   if (D < 1 || D > 8 * LS_MAXI || V < 1) return -3;
   dim3 grid(nseq, H, (V + 31) / 32);
   if (variant == 1) {
     HYB_DISPATCH(dt,
                  (lightning_scan_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)q, q_stride, (const bf16*)k, k_stride,
-                                                                    (const bf16*)v, v_stride, decay, state, meta, oraw, H, D, V)),
+                                                                    (const bf16*)v, v_stride, decay, state, meta, oraw, H, D, V, act)),
                  (lightning_scan_kernel<float><<<grid, 256, 0, st>>>((const float*)q, q_stride, (const float*)k, k_stride,
-                                                                     (const float*)v, v_stride, decay, state, meta, oraw, H, D, V)));
+                                                                     (const float*)v, v_stride, decay, state, meta, oraw, H, D, V, act)));
     return (int)cudaGetLastError();
   }
   if (variant != 2) return -3;
-  size_t smem = ((size_t)2 * D * LC_LP + (size_t)LC_L * LC_LP + (size_t)LC_L * LC_VT + (size_t)D * LC_VT + LC_L + 1 + 3) * sizeof(float);
-  if (smem > 220 * 1024) return -3;
+  if (!ctab || !stab || !scratch || nchunks < 1) return -2;
+  size_t sm1 = ((size_t)D * LC_LP + (size_t)LC_L * LC_VT + LC_L + 1 + 3) * sizeof(float);
+  size_t sm3 = ((size_t)2 * D * LC_LP + (size_t)LC_L * LC_LP + (size_t)LC_L * LC_VT + (size_t)D * LC_VT + LC_L + 1 + 3) * sizeof(float);
+  if (sm3 > 220 * 1024) return -3;
+  dim3 cgrid(nchunks, H, (V + 31) / 32), sgrid(nseq, H, (D * V + 255) / 256);
   cudaError_t e;
   if (dt == 0) {
-    if ((e = cudaFuncSetAttribute(lightning_chunk_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
-    lightning_chunk_kernel<bf16><<<grid, 256, smem, st>>>((const bf16*)q, q_stride, (const bf16*)k, k_stride, (const bf16*)v,
-                                                          v_stride, decay, state, meta, oraw, H, D, V);
+    if ((e = cudaFuncSetAttribute(lightning_chunk_state_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm1)) != cudaSuccess) return (int)e;
+    if ((e = cudaFuncSetAttribute(lightning_chunk_out_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm3)) != cudaSuccess) return (int)e;
+    lightning_chunk_state_kernel<bf16><<<cgrid, 256, sm1, st>>>((const bf16*)k, k_stride, (const bf16*)v, v_stride, decay, ctab,
+                                                                scratch, H, D, V, act);
+    lightning_chunk_scan_kernel<<<sgrid, 256, 0, st>>>(decay, state, meta, ctab, stab, scratch, H, D, V);
+    lightning_chunk_out_kernel<bf16><<<cgrid, 256, sm3, st>>>((const bf16*)q, q_stride, (const bf16*)k, k_stride, (const bf16*)v,
+                                                              v_stride, decay, ctab, scratch, oraw, H, D, V, act);
   } else {
-    if ((e = cudaFuncSetAttribute(lightning_chunk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
-    lightning_chunk_kernel<float><<<grid, 256, smem, st>>>((const float*)q, q_stride, (const float*)k, k_stride,
-                                                           (const float*)v, v_stride, decay, state, meta, oraw, H, D, V);
+    if ((e = cudaFuncSetAttribute(lightning_chunk_state_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm1)) != cudaSuccess) return (int)e;
+    if ((e = cudaFuncSetAttribute(lightning_chunk_out_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm3)) != cudaSuccess) return (int)e;
+    lightning_chunk_state_kernel<float><<<cgrid, 256, sm1, st>>>((const float*)k, k_stride, (const float*)v, v_stride, decay,
+                                                                 ctab, scratch, H, D, V, act);
+    lightning_chunk_scan_kernel<<<sgrid, 256, 0, st>>>(decay, state, meta, ctab, stab, scratch, H, D, V);
+    lightning_chunk_out_kernel<float><<<cgrid, 256, sm3, st>>>((const float*)q, q_stride, (const float*)k, k_stride,
+                                                               (const float*)v, v_stride, decay, ctab, scratch, oraw, H, D, V, act);
   }
   return (int)cudaGetLastError();
 }
@@ -2376,38 +2442,17 @@ int hyb_norm_gate_rows(const float* o, const void* w, const void* g, long long g
 
 int hyb_gated_sum_norm(const void* a, long long a_stride, const void* b, long long b_stride, const void* sg,
                        long long sg_stride, const void* w, float* resid, long long r_stride, int rows, int n, float eps,
-                       int kind, int dt, cudaStream_t st) {
+                       int kind, void* copy, int dt, cudaStream_t st) {
   if (rows == 0) return 0;
   if (kind < 0 || kind > 1 || !w) return -3;
   HYB_DISPATCH(dt,
                (gated_sum_norm_kernel<bf16><<<rows, 256, 0, st>>>((const bf16*)a, a_stride, (const bf16*)b, b_stride,
                                                                   (const bf16*)sg, sg_stride, (const bf16*)w, resid, r_stride,
-                                                                  n, eps, kind)),
+                                                                  n, eps, kind, (bf16*)copy)),
                (gated_sum_norm_kernel<float><<<rows, 256, 0, st>>>((const float*)a, a_stride, (const float*)b, b_stride,
                                                                    (const float*)sg, sg_stride, (const float*)w, resid,
-                                                                   r_stride, n, eps, kind)));
+                                                                   r_stride, n, eps, kind, (float*)copy)));
   return (int)cudaGetLastError();
 }
 
 }  // extern "C"
-
-namespace hyb {
-// out[r, c] = silu(in[r, c]) for rows that are a column slice of a wider matrix (row stride in_stride); out is dense.
-template <typename T>
-__global__ void silu_rows_kernel(const T* __restrict__ in, long long in_stride, T* __restrict__ out, int n, long long total) {
-  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= total) return;
-  long long r = i / n;
-  int c = (int)(i - r * n);
-  out[i] = from_f<T>(siluf_(to_f(in[(size_t)r * in_stride + c])));
-}
-}  // namespace hyb
-
-extern "C" int hyb_silu_rows(const void* in, long long in_stride, void* out, int rows, int n, int dt, cudaStream_t st) {
-  long long total = (long long)rows * n;
-  if (total == 0) return 0;
-  unsigned blocks = (unsigned)((total + 255) / 256);
-  HYB_DISPATCH(dt, (silu_rows_kernel<bf16><<<blocks, 256, 0, st>>>((const bf16*)in, in_stride, (bf16*)out, n, total)),
-               (silu_rows_kernel<float><<<blocks, 256, 0, st>>>((const float*)in, in_stride, (float*)out, n, total)));
-  return (int)cudaGetLastError();
-}

@@ -27,7 +27,7 @@ import torch.nn.functional as F
 from . import build as _build
 
 __all__ = ["BatchPlan", "HybridOpsError", "lib", "embed_rows", "cast_into", "norm_rows", "norm_accumulate", "gelu_",
-           "headmajor_gate", "softcap", "silu_rows", "glu", "latent_append", "latent_attn", "causal_softmax", "matmul_f32", "conv_silu", "gated_recurrence", "linear",
+           "headmajor_gate", "softcap", "glu", "latent_append", "latent_attn", "causal_softmax", "matmul_f32", "conv_silu", "gated_recurrence", "linear",
            "rotary_inv_freq", "scaled_inv_freq", "linear_f32", "grouped_linear", "window_append", "window_attn", "head_gate", "relu2_",
            "token_side_gate", "router_topk", "moe_gemv", "gather_scale_rows", "combine_rows", "act_mul", "scaled_branches",
            "full_norm_append", "lightning_recurrence", "norm_gate_rows", "gated_sum_norm_accumulate"]
@@ -62,9 +62,8 @@ def lib() -> ctypes.CDLL:
     h.hyb_error_string.argtypes = [i32]
     h.hyb_embed_rows.argtypes = [vp, vp, vp, i32, i32, vp, vp, vp, f32, i32, vp]
     h.hyb_cast_rows.argtypes = [vp, i64, i32, vp, i64, i32, i32, i32, vp]
-    h.hyb_norm_rows.argtypes = [vp, i64, i32, vp, vp, i32, vp, i64, i32, i32, i32, f32, i32, i32, f32, f32, vp]
+    h.hyb_norm_rows.argtypes = [vp, i64, i32, vp, vp, i32, vp, i64, i32, i32, i32, f32, i32, i32, f32, f32, vp, vp]
     h.hyb_gelu_rows.argtypes = [vp, i64, i32, i32, vp]
-    h.hyb_silu_rows.argtypes = [vp, i64, vp, i32, i32, i32, vp]
     h.hyb_window_append.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp, vp, i64, vp, i32, vp]
     h.hyb_window_attn.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, i32, vp, vp, i32, i32, i32, f32, vp, i32, vp]
     h.hyb_head_gate.argtypes = [vp, vp, i64, vp, i32, i32, i32, i32, vp]
@@ -82,9 +81,9 @@ def lib() -> ctypes.CDLL:
     h.hyb_latent_attn.argtypes = [vp, vp, i64, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp, vp, i32, vp]
     h.hyb_causal_softmax.argtypes = [vp, vp, i64, i32, i32, i32, f32, i32, i32, i32, i32, f32, vp, i32, i32, vp]
     h.hyb_full_norm_append.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp, i32, vp]
-    h.hyb_lightning.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]
+    h.hyb_lightning.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp, i32, vp]
     h.hyb_norm_gate_rows.argtypes = [vp, vp, vp, i64, vp, i32, i32, f32, i32, vp]
-    h.hyb_gated_sum_norm.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, i64, i32, i32, f32, i32, i32, vp]
+    h.hyb_gated_sum_norm.argtypes = [vp, i64, vp, i64, vp, i64, vp, vp, i64, i32, i32, f32, i32, vp, i32, vp]
     h.hyb_conv_silu.argtypes = [vp, i64, vp, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, vp]
     h.hyb_gated_recurrence.argtypes = [ctypes.POINTER(_RecArgs), i32, i32, i32, i32, vp, vp, vp, vp]
     _lib = h
@@ -260,7 +259,7 @@ def norm_rows(x: torch.Tensor, w: Optional[torch.Tensor], b: Optional[torch.Tens
     ref = w if w is not None else x
     _check(lib().hyb_norm_rows(x.data_ptr(), xs, _dt(x), None if w is None else w.data_ptr(),
                                None if b is None else b.data_ptr(), _dt(ref), out.data_ptr(), n, _dt(out), x.size(0), n,
-                               eps, _NORM_KINDS[kind], 0, 1.0, float(w_offset), _st()), "norm_rows")
+                               eps, _NORM_KINDS[kind], 0, 1.0, float(w_offset), None, _st()), "norm_rows")
     return out
 
 
@@ -268,19 +267,26 @@ _NORM_KINDS = {"layer": 0, "rms": 1, "none": 2}
 
 
 def norm_accumulate(resid: torch.Tensor, y: torch.Tensor, w: Optional[torch.Tensor], b: Optional[torch.Tensor], eps: float,
-                    kind: str = "layer", scale: float = 1.0) -> None:
+                    kind: str = "layer", scale: float = 1.0, copy: Optional[torch.Tensor] = None) -> None:
     """``resid += scale * norm(y)`` in one pass over the fp32 residual: the post-norm and residual sum of a sandwich
-    block (``kind`` "layer" or "rms"), or the scaled residual sum of a pre-norm block (``kind="none"``: no norm)."""
+    block (``kind`` "layer" or "rms"), or the scaled residual sum of a pre-norm block (``kind="none"``: no norm).
+    ``copy`` (dense, the weight's type, with a norm): also receives the updated residual, rounded — what the next
+    sublayer of a post-norm block reads."""
     if resid.dtype != torch.float32:
         raise HybridOpsError("the residual stream is fp32")
     if not y.is_cuda:
         resid.add_(_norm_torch(y, w, b, eps, kind), alpha=float(scale))
+        if copy is not None:
+            copy.copy_(resid)
         return
+    if copy is not None and (w is None or copy.dtype != w.dtype or not copy.is_contiguous() or copy.shape != resid.shape):
+        raise HybridOpsError("the residual's copy is dense and has the norm weight's type")
     ys, n = _rows(y)
     ref = w if w is not None else y
     _check(lib().hyb_norm_rows(y.data_ptr(), ys, _dt(y), None if w is None else w.data_ptr(),
                                None if b is None else b.data_ptr(), _dt(ref), resid.data_ptr(), resid.stride(0), 1,
-                               y.size(0), n, eps, _NORM_KINDS[kind], 1, float(scale), 0.0, _st()), "norm_accumulate")
+                               y.size(0), n, eps, _NORM_KINDS[kind], 1, float(scale), 0.0,
+                               None if copy is None else copy.data_ptr(), _st()), "norm_accumulate")
 
 
 def gelu_(x: torch.Tensor) -> torch.Tensor:
@@ -290,16 +296,6 @@ def gelu_(x: torch.Tensor) -> torch.Tensor:
     assert x.is_contiguous()
     _check(lib().hyb_gelu_rows(x.data_ptr(), x.numel(), _dt(x), 0, _st()), "gelu")
     return x
-
-
-def silu_rows(x: torch.Tensor) -> torch.Tensor:
-    """``silu(x)`` of rows that may be a column slice of a wider matrix, evaluated in fp32; the result is dense."""
-    if not x.is_cuda:
-        return F.silu(x.float()).to(x.dtype)
-    xs, n = _rows(x)
-    out = torch.empty(x.size(0), n, device=x.device, dtype=x.dtype)
-    _check(lib().hyb_silu_rows(x.data_ptr(), xs, out.data_ptr(), x.size(0), n, _dt(x), _st()), "silu_rows")
-    return out
 
 
 def relu2_(x: torch.Tensor) -> torch.Tensor:
@@ -925,11 +921,13 @@ lightning_chunk_from = 16  # a step whose longest sequence brings at least this 
 
 
 def lightning_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
-                         plan: BatchPlan, heads: int, dim: int, vdim: int, variant: int = 0) -> torch.Tensor:
+                         plan: BatchPlan, heads: int, dim: int, vdim: int, variant: int = 0, act: bool = False) -> torch.Tensor:
     """``S <- decay_h S + k v^T``, ``o = S^T q`` per head and token, ``S [dim, vdim]`` fp32 in ``state[slot, head]``
     (read at the start of the step, written back at its end); no scale.  ``decay`` fp32 ``[heads]``.  Returns the raw
-    read-outs as fp32 ``[N, heads * vdim]``.  ``variant`` (CUDA): 1 the token scan, 2 chunks of 64 tokens (a chunk is
-    four small matrix products; only non-negative powers of the decay occur), 0 chooses by the longest sequence."""
+    read-outs as fp32 ``[N, heads * vdim]``.  ``act``: q, k, v are pre-activations, their SiLU is taken in fp32 as they
+    are read.  ``variant`` (CUDA): 1 the token scan; 2 chunks of 64 tokens, all chunks of the step in parallel (a chunk
+    is four small matrix products, only ``S' = decay^len S + U`` chains the chunks of a sequence, only non-negative powers
+    of the decay occur); 0 chooses by the longest sequence."""
     N = v.size(0)
     H, D, V = heads, dim, vdim
     if state.dtype != torch.float32 or decay.dtype != torch.float32:
@@ -937,6 +935,8 @@ def lightning_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, deca
     if not q.is_cuda:
         out = torch.empty(N, H * V, dtype=torch.float32)
         qf, kf, vf = q.float().reshape(N, H, D), k.float().reshape(N, H, D), v.float().reshape(N, H, V)
+        if act:
+            qf, kf, vf = F.silu(qf), F.silu(kf), F.silu(vf)
         lam = decay.float()[:, None, None]
         for r0, n, slot, _ in plan.seqs:
             S = state[slot].clone()
@@ -948,9 +948,24 @@ def lightning_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, deca
     if not variant:
         variant = 2 if max(n for _, n, _, _ in plan.seqs) >= lightning_chunk_from else 1
     out = torch.empty(N, H * V, device=v.device, dtype=torch.float32)
+    ctab = stab = scratch = None
+    nchunks = 0
+    if variant == 2:
+        tabs = plan.shared.get("lightning_chunks")  # the same for every such layer of the step
+        if tabs is None:
+            chunks, per_seq = [], []
+            for i, (r0, n, _, _) in enumerate(plan.seqs):
+                per_seq.append((len(chunks), (n + 63) // 64))
+                chunks += [(r0 + c, min(64, n - c), i, 0) for c in range(0, n, 64)]
+            tabs = (torch.tensor(chunks, dtype=torch.int32).to(v.device), torch.tensor(per_seq, dtype=torch.int32).to(v.device), len(chunks))
+            plan.shared["lightning_chunks"] = tabs
+        ctab, stab, nchunks = tabs
+        scratch = torch.empty(nchunks, H, D, V, device=v.device, dtype=torch.float32)
     _check(lib().hyb_lightning(q.data_ptr(), _rows(q)[0], k.data_ptr(), _rows(k)[0], v.data_ptr(), _rows(v)[0],
                                decay.data_ptr(), state.data_ptr(), plan.meta.data_ptr(), out.data_ptr(), len(plan.seqs),
-                               H, D, V, int(variant), _dt(v), _st()), "lightning_recurrence")
+                               H, D, V, int(variant), int(bool(act)), None if ctab is None else ctab.data_ptr(),
+                               None if stab is None else stab.data_ptr(), nchunks,
+                               None if scratch is None else scratch.data_ptr(), _dt(v), _st()), "lightning_recurrence")
     return out
 
 
@@ -967,18 +982,23 @@ def norm_gate_rows(o: torch.Tensor, w: torch.Tensor, g: torch.Tensor, eps: float
 
 
 def gated_sum_norm_accumulate(resid: torch.Tensor, a: torch.Tensor, b: Optional[torch.Tensor], sg: Optional[torch.Tensor],
-                              w: torch.Tensor, eps: float, kind: str = "rms") -> None:
+                              w: torch.Tensor, eps: float, kind: str = "rms", copy: Optional[torch.Tensor] = None) -> None:
     """``resid += norm(a + sigmoid(sg) * b) * w`` in one pass over the fp32 residual: ``a`` and ``b`` are two branches
-    of a feed-forward, ``sg [N, 1]`` one gate logit per token for ``b`` (absent: 1).  All sums are fp32."""
+    of a feed-forward, ``sg [N, 1]`` one gate logit per token for ``b`` (absent: 1).  All sums are fp32.  ``copy``: as in
+    :func:`norm_accumulate`."""
     if resid.dtype != torch.float32:
         raise HybridOpsError("the residual stream is fp32")
     if b is None:
-        return norm_accumulate(resid, a, w, None, eps, kind)
+        return norm_accumulate(resid, a, w, None, eps, kind, copy=copy)
     if not a.is_cuda:
         y = a.float() + (torch.sigmoid(sg.float()) if sg is not None else 1.0) * b.float()
         resid.add_(_norm_torch(y, w, None, eps, kind))
+        if copy is not None:
+            copy.copy_(resid)
         return
+    if copy is not None and (copy.dtype != a.dtype or not copy.is_contiguous() or copy.shape != resid.shape):
+        raise HybridOpsError("the residual's copy is dense and has the activation type")
     _check(lib().hyb_gated_sum_norm(a.data_ptr(), _rows(a)[0], b.data_ptr(), _rows(b)[0],
                                     None if sg is None else sg.data_ptr(), 0 if sg is None else sg.stride(0), w.data_ptr(),
                                     resid.data_ptr(), resid.stride(0), a.size(0), a.size(1), float(eps),
-                                    _NORM_KINDS[kind], _dt(a), _st()), "gated_sum_norm")
+                                    _NORM_KINDS[kind], None if copy is None else copy.data_ptr(), _dt(a), _st()), "gated_sum_norm")

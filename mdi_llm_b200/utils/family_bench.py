@@ -266,8 +266,6 @@ def _zudovik_kernels(model: Any, T: int, batch: int) -> List[Dict[str, Any]]:
         ms = _time(lambda: H.embed_rows(model.embed, tok, None, plan, model.config.embed_scale), 5, 3, flush)
         rec("embed_rows[scale]", "embed_rows[positions]", phase, ms, N * C * 6.0, 0.0)
         x = torch.randn(N, C, device=dev)
-        ms = _time(lambda: model.blocks[0]._read(x, dt), 5, 3, flush)
-        rec("cast_rows", "", phase, ms, N * C * 6.0, 0.0)
         h = torch.randn(N, C, device=dev).to(dt)
         p = H.linear(h, att.w_in, att.b_in)
         q, g = att.col(p, "q"), att.col(p, "g")
@@ -295,12 +293,9 @@ def _zudovik_kernels(model: Any, T: int, batch: int) -> List[Dict[str, Any]]:
         # the recurrent mixer
         LH, LD, LV = lit.H, lit.D, lit.V
         pl = H.linear(h, lit.w_in)
-        ms = _time(lambda: H.silu_rows(pl[:, :2 * LH * LD + LH * LV]), 5, 3, flush)
-        rec("silu_rows", "act_mul", phase, ms, 4.0 * N * (2 * LH * LD + LH * LV), 0.0)
-        a = H.silu_rows(pl[:, :2 * LH * LD + LH * LV])
         state = pool.runs[1]["state"]
-        ms = _time(lambda: H.lightning_recurrence(a[:, :LH * LD], a[:, LH * LD:2 * LH * LD], a[:, 2 * LH * LD:], lit.decay, state,
-                                                  plan, LH, LD, LV), 5, 3, flush)
+        ms = _time(lambda: H.lightning_recurrence(lit.col(pl, "q"), lit.col(pl, "k"), lit.col(pl, "v"), lit.decay, state,
+                                                  plan, LH, LD, LV, act=True), 5, 3, flush)
         nbytes = 2.0 * N * (2 * LH * LD + LH * LV) + 4.0 * N * LH * LV + 8.0 * n_seq * LH * LD * LV
         rec("lightning_recurrence[chunks]" if phase == "prefill" else "lightning_recurrence[scan]", "gated_recurrence[gla]", phase,
             ms, nbytes, 4.0 * N * LH * LD * LV)
@@ -329,10 +324,11 @@ def _zudovik_kernels(model: Any, T: int, batch: int) -> List[Dict[str, Any]]:
         ya, yb = (torch.randn(N, C, device=dev).to(dt) for _ in range(2))
         sg = torch.randn(N, 1, device=dev).to(dt)
         blk = model.blocks[2]
-        ms = _time(lambda: H.norm_accumulate(x, ya, blk.norm1.w, None, 1e-6, "rms"), 5, 3, flush)
-        rec("post_norm_accumulate", "scaled_branches", phase, ms, N * C * 10.0, 0.0)
-        ms = _time(lambda: H.gated_sum_norm_accumulate(x, ya, yb, sg, blk.norm2.w, 1e-6), 5, 3, flush)
-        rec("gated_sum_norm_accumulate", "scaled_branches", phase, ms, N * C * 12.0, 0.0)
+        cp = torch.empty(N, C, device=dev, dtype=dt)
+        ms = _time(lambda: H.norm_accumulate(x, ya, blk.norm1.w, None, 1e-6, "rms", copy=cp), 5, 3, flush)
+        rec("post_norm_accumulate[+ rounded copy]", "scaled_branches", phase, ms, N * C * 12.0, 0.0)
+        ms = _time(lambda: H.gated_sum_norm_accumulate(x, ya, yb, sg, blk.norm2.w, 1e-6, copy=cp), 5, 3, flush)
+        rec("gated_sum_norm_accumulate[+ rounded copy]", "scaled_branches", phase, ms, N * C * 14.0, 0.0)
         del pool
     return rows
 
