@@ -2203,20 +2203,35 @@ __global__ void __launch_bounds__(256) lightning_chunk_state_kernel(const T* __r
 __global__ void lightning_chunk_scan_kernel(const float* __restrict__ decay, float* __restrict__ state,
                                             const int* __restrict__ meta, const int* __restrict__ ctab,
                                             const int* __restrict__ stab, float* __restrict__ scratch, int H, int D, int V) {
+  // One thread per element of the [D, V] state.  Only the multiply-add chains the chunks: the U of eight chunks are
+  // loaded together (independent loads in flight), then folded in order while the states before them are stored.
+  __shared__ float s_full, s_last;
   int seq = blockIdx.x, h = blockIdx.y;
-  int e = blockIdx.z * blockDim.x + threadIdx.x;  // element of the [D, V] state
-  if (e >= D * V) return;
   int slot = meta[4 * seq + 2], c0 = stab[2 * seq], nc = stab[2 * seq + 1];
-  double lam = (double)decay[h];
-  float full = (float)pow(lam, (double)LC_L);
+  if (threadIdx.x == 0) {
+    double lam = (double)decay[h];
+    s_full = (float)pow(lam, (double)LC_L);
+    s_last = (float)pow(lam, (double)ctab[4 * (c0 + nc - 1) + 1]);  // only a sequence's last chunk can be short
+  }
+  __syncthreads();
+  int e = blockIdx.z * blockDim.x + threadIdx.x;
+  if (e >= D * V) return;
+  const float full = s_full, last = s_last;
+  const size_t cs = (size_t)H * D * V;  // floats between the same element of consecutive chunks
   float* sp = state + (((size_t)slot * H + h) * D) * V + e;
+  float* u = scratch + (((size_t)c0 * H + h) * D) * V + e;
   float S = *sp;
-  for (int c = c0; c < c0 + nc; ++c) {
-    float* u = scratch + (((size_t)c * H + h) * D) * V + e;
-    int len = ctab[4 * c + 1];
-    float U = *u;
-    *u = S;  // the state before chunk c
-    S = (len == LC_L ? full : (float)pow(lam, (double)len)) * S + U;
+  for (int c = 0; c < nc; c += 8) {
+    float U[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) U[i] = c + i < nc ? u[(size_t)(c + i) * cs] : 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (c + i < nc) {
+        u[(size_t)(c + i) * cs] = S;  // the state before chunk c + i
+        S = (c + i == nc - 1 ? last : full) * S + U[i];
+      }
+    }
   }
   *sp = S;
 }
