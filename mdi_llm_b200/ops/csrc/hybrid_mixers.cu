@@ -2140,62 +2140,88 @@ __global__ void __launch_bounds__(256) lightning_scan_kernel(const T* __restrict
 // of a sequence.  Powers of lam only have non-negative exponents, so nothing overflows however small lam is.  Three
 // kernels over a chunk table ctab[c] = {first token row, tokens, sequence, 0} (chunks of a sequence in order) and
 // stab[seq] = {first chunk, chunks}:
-//   lightning_chunk_state_kernel  grid (chunk, head, 32-column tile of V): U_c = sum_s lam^(len-1-s) k_s v_s^T -> scratch
+//   lightning_chunk_state_kernel  grid (chunk, head): U_c = sum_s lam^(len-1-s) k_s v_s^T -> scratch
 //   lightning_chunk_scan_kernel   grid (sequence, head, slices of D*V): walks the sequence's chunks, replaces U_c by the
 //                                 state BEFORE chunk c and leaves the final state in the slot
-//   lightning_chunk_out_kernel    grid (chunk, head, tile of V): decayed causal scores, weighted values, read-out of
-//                                 the state before the chunk
-// Everything is fp32 in shared memory: Q and K of the chunk transposed ([D][68]), the scores transposed ([s][t]), the V
-// tile, the state tile [D][32].  The scores are recomputed by each column tile of a head; they are a small part of a
-// chunk's arithmetic.  scratch is [chunks, H, D, V] fp32.
+//   lightning_chunk_out_kernel    grid (chunk, head): decayed causal scores, weighted values, read-out of the state
+//                                 before the chunk
+// Everything is fp32 in shared memory: Q and K of the chunk transposed ([D][68]), the scores transposed ([s][t]), and per
+// 32-column tile of V the value tile and the state tile [D][32].  A block loads Q and K and computes the scores once and
+// walks the column tiles.  vec != 0 (rows 16-byte aligned, D a multiple of 8): a lane owns a token and fetches 8
+// channels per load, so the transposed stores hit 32 different banks.  scratch is [chunks, H, D, V] fp32.
 #define LC_L 64
 #define LC_LP 68
 #define LC_VT 32
+// dst[d][t] = act(src[row0 + t, h * D + d]) for t < len, zero for the rest of the chunk (dst is [D][LC_LP]).
+template <typename T>
+__device__ __forceinline__ void load_chunk_transposed(float* __restrict__ dst, const T* __restrict__ src, long long stride,
+                                                      int row0, int len, int h, int D, int act, int vec) {
+  if (vec) {
+    int d8n = D >> 3;
+    for (int i = threadIdx.x; i < LC_L * d8n; i += 256) {
+      int t = i & (LC_L - 1), d8 = i >> 6;  // a warp: 32 tokens of one group of 8 channels
+      float f[8];
+      if (t < len) {
+        load8(src + (size_t)(row0 + t) * stride + (size_t)h * D + d8 * 8, f);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = 0.f;
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dst[(d8 * 8 + e) * LC_LP + t] = t < len ? lin_act(f[e], act) : 0.f;
+    }
+    return;
+  }
+  for (int i = threadIdx.x; i < LC_L * D; i += 256) {
+    int t = i / D, d = i - t * D;
+    dst[d * LC_LP + t] = t < len ? lin_act(to_f(src[(size_t)(row0 + t) * stride + (size_t)h * D + d]), act) : 0.f;
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) lightning_chunk_state_kernel(const T* __restrict__ k, long long k_stride,
                                                                     const T* __restrict__ v, long long v_stride,
                                                                     const float* __restrict__ decay,
                                                                     const int* __restrict__ ctab, float* __restrict__ scratch,
-                                                                    int H, int D, int V, int act) {
+                                                                    int H, int D, int V, int act, int vec) {
   extern __shared__ __align__(16) float lsm[];
   float* Kt = lsm;                       // [D][LC_LP]
   float* Vs = Kt + (size_t)D * LC_LP;    // [LC_L][LC_VT], already times lam^(len-1-s)
   float* pw = Vs + LC_L * LC_VT;         // [LC_L + 1]
   const int* c = ctab + 4 * blockIdx.x;
   int row0 = c[0], len = c[1];
-  int h = blockIdx.y, v0 = blockIdx.z * LC_VT;
+  int h = blockIdx.y;
   int tid = threadIdx.x, lane = tid & 31, tg = tid >> 5;
   for (int i = tid; i <= LC_L; i += 256) pw[i] = (float)pow((double)decay[h], (double)i);
-  __syncthreads();
-  for (int i = tid; i < LC_L * D; i += 256) {
-    int t = i / D, d = i - t * D;
-    Kt[d * LC_LP + t] = t < len ? lin_act(to_f(k[(size_t)(row0 + t) * k_stride + (size_t)h * D + d]), act) : 0.f;
-  }
-  for (int i = tid; i < LC_L * LC_VT; i += 256) {
-    int t = i >> 5, cc = i & 31;
-    Vs[i] = t < len && v0 + cc < V ? lin_act(to_f(v[(size_t)(row0 + t) * v_stride + (size_t)h * V + v0 + cc]), act) * pw[len - 1 - t] : 0.f;
-  }
-  __syncthreads();
+  load_chunk_transposed(Kt, k, k_stride, row0, len, h, D, act, vec);
   float* up = scratch + (((size_t)blockIdx.x * H + h) * D) * V;
-  // thread (lane, tg) owns column lane of rows d = tg + 8 i, four rows at a time
-  for (int i0 = 0; tg + 8 * i0 < D; i0 += 4) {
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    int dd[4];
+  for (int v0 = 0; v0 < V; v0 += LC_VT) {
+    __syncthreads();  // pw and Kt are written; the previous tile is done with Vs
+    for (int i = tid; i < LC_L * LC_VT; i += 256) {
+      int t = i >> 5, cc = i & 31;
+      Vs[i] = t < len && v0 + cc < V ? lin_act(to_f(v[(size_t)(row0 + t) * v_stride + (size_t)h * V + v0 + cc]), act) * pw[len - 1 - t] : 0.f;
+    }
+    __syncthreads();
+    // thread (lane, tg) owns column lane of rows d = tg + 8 i, four rows at a time
+    for (int i0 = 0; tg + 8 * i0 < D; i0 += 4) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      int dd[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) dd[u] = min(tg + 8 * (i0 + u), D - 1);  // rows past D: computed, not stored
-    for (int s0 = 0; s0 < len; s0 += 4) {  // rows of Kt and Vs are zero past len
-      float w0 = Vs[s0 * LC_VT + lane], w1 = Vs[(s0 + 1) * LC_VT + lane], w2 = Vs[(s0 + 2) * LC_VT + lane],
-            w3 = Vs[(s0 + 3) * LC_VT + lane];
+      for (int u = 0; u < 4; ++u) dd[u] = min(tg + 8 * (i0 + u), D - 1);  // rows past D: computed, not stored
+      for (int s0 = 0; s0 < len; s0 += 4) {  // rows of Kt and Vs are zero past len
+        float w0 = Vs[s0 * LC_VT + lane], w1 = Vs[(s0 + 1) * LC_VT + lane], w2 = Vs[(s0 + 2) * LC_VT + lane],
+              w3 = Vs[(s0 + 3) * LC_VT + lane];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          float4 kv = *reinterpret_cast<const float4*>(Kt + dd[u] * LC_LP + s0);
+          acc[u] += kv.x * w0 + kv.y * w1 + kv.z * w2 + kv.w * w3;
+        }
+      }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        float4 kv = *reinterpret_cast<const float4*>(Kt + dd[u] * LC_LP + s0);
-        acc[u] += kv.x * w0 + kv.y * w1 + kv.z * w2 + kv.w * w3;
+        int d = tg + 8 * (i0 + u);
+        if (d < D && v0 + lane < V) up[(size_t)d * V + v0 + lane] = acc[u];
       }
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      int d = tg + 8 * (i0 + u);
-      if (d < D && v0 + lane < V) up[(size_t)d * V + v0 + lane] = acc[u];
     }
   }
 }
@@ -2243,7 +2269,7 @@ __global__ void __launch_bounds__(256) lightning_chunk_out_kernel(const T* __res
                                                                   const float* __restrict__ decay,
                                                                   const int* __restrict__ ctab,
                                                                   const float* __restrict__ scratch, float* __restrict__ oraw,
-                                                                  int H, int D, int V, int act) {
+                                                                  int H, int D, int V, int act, int vec) {
   extern __shared__ __align__(16) float lsm[];
   float* Qt = lsm;                       // [D][LC_LP]
   float* Kt = Qt + (size_t)D * LC_LP;    // [D][LC_LP]
@@ -2253,26 +2279,12 @@ __global__ void __launch_bounds__(256) lightning_chunk_out_kernel(const T* __res
   float* pw = Ss + (size_t)D * LC_VT;    // [LC_L + 1]: lam^i
   const int* c = ctab + 4 * blockIdx.x;
   int row0 = c[0], len = c[1];
-  int h = blockIdx.y, v0 = blockIdx.z * LC_VT;
+  int h = blockIdx.y;
   int tid = threadIdx.x, lane = tid & 31, tg = tid >> 5;
-  int vc = v0 + lane;
-  bool live = vc < V;
   const float* sp = scratch + (((size_t)blockIdx.x * H + h) * D) * V;
   for (int i = tid; i <= LC_L; i += 256) pw[i] = (float)pow((double)decay[h], (double)i);
-  for (int i = tid; i < D * LC_VT; i += 256) {
-    int d = i >> 5, cc = i & 31;
-    Ss[i] = v0 + cc < V ? sp[(size_t)d * V + v0 + cc] : 0.f;
-  }
-  for (int i = tid; i < LC_L * D; i += 256) {
-    int t = i / D, d = i - t * D;
-    size_t row = (size_t)(row0 + t);
-    Qt[d * LC_LP + t] = t < len ? lin_act(to_f(q[row * q_stride + (size_t)h * D + d]), act) : 0.f;
-    Kt[d * LC_LP + t] = t < len ? lin_act(to_f(k[row * k_stride + (size_t)h * D + d]), act) : 0.f;
-  }
-  for (int i = tid; i < LC_L * LC_VT; i += 256) {
-    int t = i >> 5, cc = i & 31;
-    Vs[i] = t < len && v0 + cc < V ? lin_act(to_f(v[(size_t)(row0 + t) * v_stride + (size_t)h * V + v0 + cc]), act) : 0.f;
-  }
+  load_chunk_transposed(Qt, q, q_stride, row0, len, h, D, act, vec);
+  load_chunk_transposed(Kt, k, k_stride, row0, len, h, D, act, vec);
   __syncthreads();
   int ty = tid >> 4, tx = tid & 15;
   {  // scores: thread (ty, tx) owns t = 4 ty .. 4 ty + 3 against s = 4 tx .. 4 tx + 3
@@ -2305,7 +2317,19 @@ __global__ void __launch_bounds__(256) lightning_chunk_out_kernel(const T* __res
     }
   }
   __syncthreads();
-  {  // outputs: thread (lane, tg) owns column v0 + lane of rows t = 8 tg .. 8 tg + 7
+  for (int v0 = 0; v0 < V; v0 += LC_VT) {
+    int vc = v0 + lane;
+    bool live = vc < V;
+    for (int i = tid; i < D * LC_VT; i += 256) {
+      int d = i >> 5, cc = i & 31;
+      Ss[i] = v0 + cc < V ? sp[(size_t)d * V + v0 + cc] : 0.f;
+    }
+    for (int i = tid; i < LC_L * LC_VT; i += 256) {
+      int t = i >> 5, cc = i & 31;
+      Vs[i] = t < len && v0 + cc < V ? lin_act(to_f(v[(size_t)(row0 + t) * v_stride + (size_t)h * V + v0 + cc]), act) : 0.f;
+    }
+    __syncthreads();
+    // outputs: thread (lane, tg) owns column v0 + lane of rows t = 8 tg .. 8 tg + 7
     float in[8], st[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) in[i] = st[i] = 0.f;
@@ -2331,6 +2355,7 @@ __global__ void __launch_bounds__(256) lightning_chunk_out_kernel(const T* __res
         if (t < len) oraw[(size_t)(row0 + t) * H * V + (size_t)h * V + vc] = in[i] + pw[t + 1] * st[i];
       }
     }
+    __syncthreads();  // the next tile overwrites Vs and Ss
   }
 }
 
@@ -2425,24 +2450,26 @@ int hyb_lightning(const void* q, long long q_stride, const void* k, long long k_
   size_t sm1 = ((size_t)D * LC_LP + (size_t)LC_L * LC_VT + LC_L + 1 + 3) * sizeof(float);
   size_t sm3 = ((size_t)2 * D * LC_LP + (size_t)LC_L * LC_LP + (size_t)LC_L * LC_VT + (size_t)D * LC_VT + LC_L + 1 + 3) * sizeof(float);
   if (sm3 > 220 * 1024) return -3;
-  dim3 cgrid(nchunks, H, (V + 31) / 32), sgrid(nseq, H, (D * V + 255) / 256);
+  dim3 cgrid(nchunks, H), sgrid(nseq, H, (D * V + 255) / 256);
+  // 16-byte loads of q and k rows: every head's slice of every row starts on a 16-byte boundary
+  int vec = D % 8 == 0 && q_stride % 8 == 0 && k_stride % 8 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)k % 16 == 0;
   cudaError_t e;
   if (dt == 0) {
     if ((e = cudaFuncSetAttribute(lightning_chunk_state_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm1)) != cudaSuccess) return (int)e;
     if ((e = cudaFuncSetAttribute(lightning_chunk_out_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm3)) != cudaSuccess) return (int)e;
     lightning_chunk_state_kernel<bf16><<<cgrid, 256, sm1, st>>>((const bf16*)k, k_stride, (const bf16*)v, v_stride, decay, ctab,
-                                                                scratch, H, D, V, act);
+                                                                scratch, H, D, V, act, vec);
     lightning_chunk_scan_kernel<<<sgrid, 256, 0, st>>>(decay, state, meta, ctab, stab, scratch, H, D, V);
     lightning_chunk_out_kernel<bf16><<<cgrid, 256, sm3, st>>>((const bf16*)q, q_stride, (const bf16*)k, k_stride, (const bf16*)v,
-                                                              v_stride, decay, ctab, scratch, oraw, H, D, V, act);
+                                                              v_stride, decay, ctab, scratch, oraw, H, D, V, act, vec);
   } else {
     if ((e = cudaFuncSetAttribute(lightning_chunk_state_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm1)) != cudaSuccess) return (int)e;
     if ((e = cudaFuncSetAttribute(lightning_chunk_out_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm3)) != cudaSuccess) return (int)e;
     lightning_chunk_state_kernel<float><<<cgrid, 256, sm1, st>>>((const float*)k, k_stride, (const float*)v, v_stride, decay,
-                                                                 ctab, scratch, H, D, V, act);
+                                                                 ctab, scratch, H, D, V, act, vec);
     lightning_chunk_scan_kernel<<<sgrid, 256, 0, st>>>(decay, state, meta, ctab, stab, scratch, H, D, V);
     lightning_chunk_out_kernel<float><<<cgrid, 256, sm3, st>>>((const float*)q, q_stride, (const float*)k, k_stride,
-                                                               (const float*)v, v_stride, decay, ctab, scratch, oraw, H, D, V, act);
+                                                               (const float*)v, v_stride, decay, ctab, scratch, oraw, H, D, V, act, vec);
   }
   return (int)cudaGetLastError();
 }

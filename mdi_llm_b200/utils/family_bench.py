@@ -44,15 +44,15 @@ def zudovik_bench_config(width: int) -> Dict[str, Any]:
     the third layer's keys and values + experts.  Two of eight clamped experts of width ``width`` plus two identity
     outputs in the router, and a token-gated shared expert of width ``width`` (the parallel-block design's expert sizes)."""
     h = width // 128
-    att = {"heads": h, "kv_heads": max(1, h // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
-           "rot": {"dims": 64, "base": 250000.0}}
+    att = {"heads": h, "kv_heads": max(1, h // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0,
+           "rot": {"dims": 64, "base": 500000.0}}
     lit = {"heads": h, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-3 - 5 * i / max(1, h - 1)) for i in range(h)]}
     moe = {"kind": "moe", "expert": {"ff": width, "limit": 7.0}, "router": {"experts": 8, "identity": 2, "top": 2},
            "shared": {"ff": width, "limit": 7.0}}
     layers = [{"type": "attention", "mixer": dict(att), "mlp": {"kind": "dense", "ff": 4 * width}},
               {"type": "lightning", "mixer": lit, "mlp": dict(moe)}, {"type": "attention", "mixer": dict(att), "mlp": dict(moe)},
               {"type": "attention", "mixer": {**att, "kv_from": 2}, "mlp": dict(moe)}]
-    return {"architecture": "Zudovik", "vocab": 32000, "width": width, "embedding": {"scale": width ** 0.5}, "layers": layers,
+    return {"architecture": "Zudovik", "vocab": 32000, "width": width, "embedding": {"scale": 32.0}, "layers": layers,
             "norm": {"eps": 1e-6}}
 
 

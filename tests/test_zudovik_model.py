@@ -367,7 +367,7 @@ RECURRENCE_DEVICES = [pytest.param(("cpu", 0), id="cpu"), pytest.param(("cuda", 
 
 
 @pytest.mark.parametrize("where", RECURRENCE_DEVICES)
-@pytest.mark.parametrize("sizes", [(3, 12, 20), (1, 32, 32), (2, 5, 36), (2, 40, 3), (1, 130, 70)], ids=str)
+@pytest.mark.parametrize("sizes", [(3, 12, 20), (1, 32, 32), (2, 16, 40), (2, 5, 36), (2, 40, 3), (1, 130, 70)], ids=str)
 def test_recurrence_in_steps_of_every_size_with_state_carried_in_slots(where, sizes):
     """Three sequences in slots 2, 0, 1 advance together through steps of unequal sizes (one token, two, just below, at
     and above the chunk of 64 and the switch between the two kernels) and must match the plain loops at every token;
