@@ -566,6 +566,8 @@ class MoEFF(nn.Module):
         self.E, self.top, self.ff, self.identity = int(experts), int(top), int(ff), int(identity)
         self.mode, self.gated = router, expert in ("gated_silu", "clamped")
         self.act, self.limit = ("clamped" if expert == "clamped" else "silu"), float(limit)
+        if self.identity and not self.gated:
+            raise ValueError("identity experts are implemented for gated experts (the routing weight scales the output)")
         self.router = _param(self.E + self.identity, width)
         self.router_b = _param(self.E + self.identity) if router_bias else None
         self.correction = _param(self.E + self.identity) if router == "softmax_all" else None
@@ -625,8 +627,6 @@ class MoEFF(nn.Module):
             mid = H.act_mul(H.grouped_linear(H.gather_scale_rows(h, rows), self.up, counts), self.act, self.limit)
             ident = (idx, self.E, h) if self.identity else ()
             return H.combine_rows(H.grouped_linear(mid, self.down, counts), where.to(torch.int32), N, top, wt, *ident)
-        if self.identity:
-            raise NotImplementedError("identity experts are implemented for gated experts")
         xin = H.gather_scale_rows(h, rows, wt.view(-1)[order].contiguous())
         y = H.grouped_linear(H.relu2_(H.grouped_linear(xin, self.up, counts)), self.down, counts)
         return H.combine_rows(y, where.to(torch.int32), N, top)
